@@ -33,9 +33,10 @@ class CacheGroupSpec:
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None      # None: every token is kept
+    planes: int = 2                   # rows of head_dim a head keeps per token: keys and values, or one shared row
 
     def key(self) -> tuple:
-        return (self.num_kv_heads, self.head_dim, self.window)
+        return (self.num_kv_heads, self.head_dim, self.window, self.planes)
 
 
 class PagePool:
@@ -279,9 +280,9 @@ class CacheManager:
 
 
 def group_runs(needs: Dict[int, "object"]) -> List[CacheGroupSpec]:
-    """Group runs by (kv heads, head size, window): runs with equal needs share pages ids and tables."""
+    """Group runs by (kv heads, head size, window, planes): runs with equal needs share pages ids and tables."""
     by_key: Dict[tuple, List[int]] = {}
     for run in sorted(needs):
         n = needs[run]
-        by_key.setdefault((n.num_kv_heads, n.head_dim, n.window), []).append(run)
-    return [CacheGroupSpec(tuple(runs), k[0], k[1], k[2]) for k, runs in by_key.items()]
+        by_key.setdefault((n.num_kv_heads, n.head_dim, n.window, getattr(n, "planes", 2)), []).append(run)
+    return [CacheGroupSpec(tuple(runs), k[0], k[1], k[2], k[3]) for k, runs in by_key.items()]

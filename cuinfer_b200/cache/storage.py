@@ -1,9 +1,9 @@
 """Device memory behind the cache manager's page ids and state slots.
 
 The reference keeps one pool ``[L, 2, num_blocks, block_size, n_kv, d]`` (csrc/executor/kv_cache.cpp:9-25).
-Here every cache group has a pool ``[runs, pages, 2, n_kv, page_size, d]``: the keys (or values) of one
-page and one kv head are ``page_size * d`` contiguous elements, which is the tile an attention kernel
-loads.  Per-request state of fixed size lives in ``[slots, *shape]`` tensors, one per run that asks for it.
+Here every cache group has a pool ``[runs, pages, planes, n_kv, page_size, d]`` (planes: keys and values, or the one
+row of a mixer that caches a latent): the keys (or values) of one page and one kv head are ``page_size * d``
+contiguous elements, which is the tile an attention kernel loads.  Per-request state of fixed size lives in ``[slots, *shape]`` tensors, one per run that asks for it.
 """
 from __future__ import annotations
 
@@ -20,7 +20,7 @@ _STATE_DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, "int32": 
 def page_bytes(group: CacheGroupSpec, page_size: int, dtype: torch.dtype) -> int:
     """Bytes one page id stands for: keys and values of every run of the group."""
     width = torch.empty((), dtype=dtype).element_size()
-    return len(group.runs) * 2 * group.num_kv_heads * page_size * group.head_dim * width
+    return len(group.runs) * group.planes * group.num_kv_heads * page_size * group.head_dim * width
 
 
 class CacheStorage:
@@ -32,7 +32,7 @@ class CacheStorage:
         self.run_cache: Dict[int, torch.Tensor] = {}
         self.run_group: Dict[int, int] = {}
         for g, (spec, pages) in enumerate(zip(groups, num_pages)):
-            pool = torch.zeros((len(spec.runs), pages, 2, spec.num_kv_heads, page_size, spec.head_dim),
+            pool = torch.zeros((len(spec.runs), pages, spec.planes, spec.num_kv_heads, page_size, spec.head_dim),
                                dtype=dtype, device=device)
             self.pools.append(pool)
             for i, run in enumerate(spec.runs):

@@ -48,11 +48,20 @@ def get_architecture(name: str) -> Architecture:
         ) from None
 
 
-def architecture_of(raw: Mapping[str, Any]) -> Architecture:
+def architecture_name(raw: Mapping[str, Any]) -> str:
+    """The architecture a ``config.json`` names: ``architectures[0]``, or a single name under ``architecture``."""
     archs = raw.get("architectures")
-    if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-        raise ConfigError("invalid model config: 'architectures' must be a non-empty list of names")
-    return get_architecture(archs[0])
+    if isinstance(archs, list) and archs and isinstance(archs[0], str):
+        return archs[0]
+    single = raw.get("architecture")
+    if archs is None and isinstance(single, str) and single:
+        return single
+    raise ConfigError("invalid model config: 'architectures' must be a non-empty list of names "
+                      "(or 'architecture' a name)")
+
+
+def architecture_of(raw: Mapping[str, Any]) -> Architecture:
+    return get_architecture(architecture_name(raw))
 
 
 def load_model_config(model_dir: str):

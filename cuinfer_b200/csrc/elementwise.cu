@@ -42,12 +42,12 @@ template <typename T> struct Vec<T, 1> {
 };
 
 // ---- embedding ---------------------------------------------------------------------------------
-// out[t, :] = table[ids[t], :] as 32-bit residual rows; an id outside the table gives a zero row
-// and raises the flag (the host rejects such ids before they get here).
+// out[t, :] = table[ids[t], :] * scale as 32-bit residual rows (the product is taken in 32 bits); an id outside the
+// table gives a zero row and raises the flag (the host rejects such ids before they get here).
 template <typename T, int V>
 __global__ void embedding_gather_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                                         float* __restrict__ out, int hidden, int vocab,
-                                        int* __restrict__ bad_flag) {
+                                        int* __restrict__ bad_flag, float scale) {
     const int t = blockIdx.x;
     const int id = ids[t];
     const bool ok = id >= 0 && id < vocab;
@@ -57,10 +57,8 @@ __global__ void embedding_gather_kernel(const int* __restrict__ ids, const T* __
     for (int i = threadIdx.x * V; i < hidden; i += blockDim.x * V) {
         float v[V];
         Vec<T, V>::load(src + i, v);
-        if (!ok) {
 #pragma unroll
-            for (int k = 0; k < V; ++k) v[k] = 0.f;
-        }
+        for (int k = 0; k < V; ++k) v[k] = ok ? v[k] * scale : 0.f;
         Vec<float, V>::store(dst + i, v);
     }
 }
@@ -199,9 +197,61 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ a
     }
 }
 
+// ---- squared ReLU ------------------------------------------------------------------------------------
+// out = max(x, 0)^2, taken in 32 bits and rounded once.
+template <typename T>
+__global__ void relu_squared_kernel(const T* __restrict__ x, T* __restrict__ out, size_t total) {
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+        const float v = fmaxf(to_f32(x[e]), 0.f);
+        out[e] = from_f32<T>(v * v);
+    }
+}
+
+// ---- sigmoid gate -------------------------------------------------------------------------------------
+// out[t, j] = x[t, j] * sigmoid(gate[t, j]) with the exact exponential; the rows of x and of gate may lie inside wider
+// rows (their strides are given), out is dense.
+template <typename T>
+__global__ void sigmoid_gate_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ gate, int gate_stride,
+                                    T* __restrict__ out, int cols, int rows) {
+    const size_t total = (size_t)rows * cols;
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = e / cols;
+        const int j = (int)(e % cols);
+        const float g = to_f32(gate[t * gate_stride + j]);
+        out[e] = from_f32<T>(to_f32(x[t * x_stride + j]) / (1.f + expf(-g)));
+    }
+}
+
 }  // namespace cib
 
 using namespace cib;
+
+static inline int flat_blocks(size_t total) {
+    size_t b = (total + 255) / 256;
+    return (int)(b > 148 * 16 ? 148 * 16 : (b ? b : 1));
+}
+
+extern "C" int cib_relu_squared(const void* x, void* out, int dtype, long long total, cudaStream_t stream) {
+    CIB_REQUIRE(total >= 0, "relu_squared: bad size");
+    if (total == 0) return 0;
+    if (dtype == kF32) relu_squared_kernel<float><<<flat_blocks(total), 256, 0, stream>>>((const float*)x, (float*)out, (size_t)total);
+    else if (dtype == kBF16) relu_squared_kernel<__nv_bfloat16><<<flat_blocks(total), 256, 0, stream>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, (size_t)total);
+    else CIB_REQUIRE(false, "relu_squared: unsupported dtype %d", dtype);
+    CIB_LAUNCH_CHECK("relu_squared");
+    return 0;
+}
+
+extern "C" int cib_sigmoid_gate(const void* x, int x_stride, const void* gate, int gate_stride, void* out, int dtype,
+                                int rows, int cols, cudaStream_t stream) {
+    CIB_REQUIRE(rows >= 0 && cols > 0 && x_stride >= cols && gate_stride >= cols, "sigmoid_gate: bad sizes rows=%d cols=%d", rows, cols);
+    if (rows == 0) return 0;
+    const size_t total = (size_t)rows * cols;
+    if (dtype == kF32) sigmoid_gate_kernel<float><<<flat_blocks(total), 256, 0, stream>>>((const float*)x, x_stride, (const float*)gate, gate_stride, (float*)out, cols, rows);
+    else if (dtype == kBF16) sigmoid_gate_kernel<__nv_bfloat16><<<flat_blocks(total), 256, 0, stream>>>((const __nv_bfloat16*)x, x_stride, (const __nv_bfloat16*)gate, gate_stride, (__nv_bfloat16*)out, cols, rows);
+    else CIB_REQUIRE(false, "sigmoid_gate: unsupported dtype %d", dtype);
+    CIB_LAUNCH_CHECK("sigmoid_gate");
+    return 0;
+}
 
 static inline int norm_threads(int hidden, int vec) {
     int per = (hidden + vec - 1) / vec;
@@ -211,7 +261,7 @@ static inline int norm_threads(int hidden, int vec) {
 }
 
 extern "C" int cib_embedding_gather(const int* ids, const void* table, int table_dtype, float* out,
-                                    int num_tokens, int hidden, int vocab, int* bad_flag,
+                                    int num_tokens, int hidden, int vocab, int* bad_flag, float scale,
                                     cudaStream_t stream) {
     CIB_REQUIRE(num_tokens >= 0 && hidden > 0 && vocab > 0, "embedding_gather: bad sizes T=%d H=%d V=%d",
                 num_tokens, hidden, vocab);
@@ -219,11 +269,11 @@ extern "C" int cib_embedding_gather(const int* ids, const void* table, int table
     const bool v4 = hidden % 4 == 0;
     const int threads = norm_threads(hidden, v4 ? 4 : 1) > 256 ? 256 : norm_threads(hidden, v4 ? 4 : 1);
     if (table_dtype == kF32) {
-        if (v4) embedding_gather_kernel<float, 4><<<num_tokens, threads, 0, stream>>>(ids, (const float*)table, out, hidden, vocab, bad_flag);
-        else embedding_gather_kernel<float, 1><<<num_tokens, threads, 0, stream>>>(ids, (const float*)table, out, hidden, vocab, bad_flag);
+        if (v4) embedding_gather_kernel<float, 4><<<num_tokens, threads, 0, stream>>>(ids, (const float*)table, out, hidden, vocab, bad_flag, scale);
+        else embedding_gather_kernel<float, 1><<<num_tokens, threads, 0, stream>>>(ids, (const float*)table, out, hidden, vocab, bad_flag, scale);
     } else if (table_dtype == kBF16) {
-        if (v4) embedding_gather_kernel<__nv_bfloat16, 4><<<num_tokens, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, hidden, vocab, bad_flag);
-        else embedding_gather_kernel<__nv_bfloat16, 1><<<num_tokens, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, hidden, vocab, bad_flag);
+        if (v4) embedding_gather_kernel<__nv_bfloat16, 4><<<num_tokens, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, hidden, vocab, bad_flag, scale);
+        else embedding_gather_kernel<__nv_bfloat16, 1><<<num_tokens, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, hidden, vocab, bad_flag, scale);
     } else {
         CIB_REQUIRE(false, "embedding_gather: unsupported table dtype %d", table_dtype);
     }

@@ -14,7 +14,13 @@ constexpr int kBM = 64, kBN = 64, kBK = 16;
 template <typename TI, typename TO>
 __global__ void __launch_bounds__(256)
 gemm_generic_kernel(const TI* __restrict__ a, int lda, const TI* __restrict__ w, int ldw,
-                    TO* __restrict__ out, int ldo, int M, int N, int K) {
+                    TO* __restrict__ out, int ldo, int M, int N, int K, long long a_batch, long long w_batch,
+                    long long o_batch) {
+    // blockIdx.z is the index of a batch of independent products (one per head, say): its operands lie the given
+    // numbers of elements apart
+    a += (size_t)blockIdx.z * a_batch;
+    w += (size_t)blockIdx.z * w_batch;
+    out += (size_t)blockIdx.z * o_batch;
     __shared__ float As[kBK][kBM + 4];
     __shared__ float Ws[kBK][kBN + 4];
     const int tid = threadIdx.x;
@@ -67,21 +73,35 @@ gemm_generic_kernel(const TI* __restrict__ a, int lda, const TI* __restrict__ w,
 
 using namespace cib;
 
-extern "C" int cib_gemm_generic(const void* a, int lda, const void* w, int ldw, int in_dtype, void* out, int ldo,
-                                int out_dtype, int M, int N, int K, cudaStream_t stream) {
-    CIB_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm: bad sizes M=%d N=%d K=%d", M, N, K);
+static int gemm_generic_launch(const void* a, int lda, long long a_batch, const void* w, int ldw, long long w_batch,
+                               int in_dtype, void* out, int ldo, long long o_batch, int out_dtype, int M, int N, int K,
+                               int batch, cudaStream_t stream) {
+    CIB_REQUIRE(M >= 0 && N > 0 && K > 0 && batch > 0, "gemm: bad sizes M=%d N=%d K=%d batch=%d", M, N, K, batch);
     CIB_REQUIRE(lda >= K && ldw >= K && ldo >= N, "gemm: leading dimensions too small (lda=%d ldw=%d ldo=%d)", lda, ldw, ldo);
     if (M == 0) return 0;
-    dim3 grid((N + kBN - 1) / kBN, (M + kBM - 1) / kBM);
-    CIB_REQUIRE(grid.y <= 65535, "gemm: M=%d too large for this kernel", M);
+    dim3 grid((N + kBN - 1) / kBN, (M + kBM - 1) / kBM, batch);
+    CIB_REQUIRE(grid.y <= 65535 && batch <= 65535, "gemm: M=%d or batch=%d too large for this kernel", M, batch);
     if (in_dtype == kF32 && out_dtype == kF32)
-        gemm_generic_kernel<float, float><<<grid, 256, 0, stream>>>((const float*)a, lda, (const float*)w, ldw, (float*)out, ldo, M, N, K);
+        gemm_generic_kernel<float, float><<<grid, 256, 0, stream>>>((const float*)a, lda, (const float*)w, ldw, (float*)out, ldo, M, N, K, a_batch, w_batch, o_batch);
     else if (in_dtype == kBF16 && out_dtype == kBF16)
-        gemm_generic_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)w, ldw, (__nv_bfloat16*)out, ldo, M, N, K);
+        gemm_generic_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)w, ldw, (__nv_bfloat16*)out, ldo, M, N, K, a_batch, w_batch, o_batch);
     else if (in_dtype == kBF16 && out_dtype == kF32)
-        gemm_generic_kernel<__nv_bfloat16, float><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)w, ldw, (float*)out, ldo, M, N, K);
+        gemm_generic_kernel<__nv_bfloat16, float><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)w, ldw, (float*)out, ldo, M, N, K, a_batch, w_batch, o_batch);
     else
         CIB_REQUIRE(false, "gemm: unsupported dtypes in=%d out=%d", in_dtype, out_dtype);
     CIB_LAUNCH_CHECK("gemm_generic");
     return 0;
+}
+
+extern "C" int cib_gemm_generic(const void* a, int lda, const void* w, int ldw, int in_dtype, void* out, int ldo,
+                                int out_dtype, int M, int N, int K, cudaStream_t stream) {
+    return gemm_generic_launch(a, lda, 0, w, ldw, 0, in_dtype, out, ldo, 0, out_dtype, M, N, K, 1, stream);
+}
+
+// `batch` independent products out[b] = a[b] . w[b]^T whose operands lie a_batch / w_batch / o_batch elements apart
+// (heads side by side inside wider rows: the batch stride is then smaller than the leading dimension).
+extern "C" int cib_gemm_generic_batched(const void* a, int lda, long long a_batch, const void* w, int ldw,
+                                        long long w_batch, int in_dtype, void* out, int ldo, long long o_batch,
+                                        int out_dtype, int M, int N, int K, int batch, cudaStream_t stream) {
+    return gemm_generic_launch(a, lda, a_batch, w, ldw, w_batch, in_dtype, out, ldo, o_batch, out_dtype, M, N, K, batch, stream);
 }

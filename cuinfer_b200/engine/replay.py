@@ -27,7 +27,7 @@ from .runner import ModelRunner, StepEntry
 TRACE_TOKEN_ROUNDING = 64
 
 
-def make_runner(model_dir: str, dtype: str, max_tokens: int, block_size: int = 16, max_live: int = 8,
+def make_runner(model_dir: str, dtype: str, max_tokens: int, block_size: int = 16, max_live: int = 4,
                 cuda_graph: bool = False) -> ModelRunner:
     """A runner whose page pool holds exactly ``max_tokens`` tokens (rounded up to whole pages).
     ``cuda_graph``: steps go the way generation sends them — a step of single tokens that all want their logits

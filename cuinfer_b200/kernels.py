@@ -67,7 +67,17 @@ _P, _I, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
 
 def _declare(lib: ctypes.CDLL) -> None:
     sig = {
-        "cib_embedding_gather": [_P, _P, _I, _P, _I, _I, _I, _P, _P],
+        "cib_embedding_gather": [_P, _P, _I, _P, _I, _I, _I, _P, _F, _P],
+        "cib_sandwich_layernorm": [_P, _P, _I, _P, _P, _F, _P, _P, _P, _F, _I, _P, _I, _I, _I, _P],
+        "cib_relu_squared": [_P, _P, _I, ctypes.c_longlong, _P],
+        "cib_sigmoid_gate": [_P, _I, _P, _I, _P, _I, _I, _I, _P],
+        "cib_latent_prep": [_P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _I, _F, _P, _P, _I, _P, _P, ctypes.c_longlong, _P, _I, _I, _P],
+        "cib_latent_attention_generic": [_P, _I, _I, _P, _I, _I, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _P, _P, _P, _I, _P, _I,
+                                         _I, _I, _I, _I, _F, _I, _P],
+        "cib_gemm_generic_batched": [_P, _I, ctypes.c_longlong, _P, _I, ctypes.c_longlong, _I, _P, _I, ctypes.c_longlong, _I,
+                                     _I, _I, _I, _I, _P],
+        "cib_moe_table_gate_up": [_P, _I, _I, _P, _P, _I, _I, _I, _P, _P, _I, _I, _I, _P],
+        "cib_moe_table_down": [_P, _I, _P, _P, _I, _I, _I, _P, _P, _I, _F, _P, _I, _I, _I, _P],
         "cib_add_rmsnorm": [_P, _P, _I, _P, _I, _F, _P, _I, _I, _I, _P],
         "cib_gather_rows": [_P, _P, _I, _P, _P, _I, _I, _I, _P],
         "cib_silu_mul": [_P, _P, _I, _I, _I, _P],
@@ -147,15 +157,16 @@ def _count() -> None:
 
 # ---- row-wise kernels ----------------------------------------------------------------------------
 
-def embedding_gather(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, bad_flag: torch.Tensor | None = None) -> None:
-    """out[t] = table[ids[t]] as float32 rows."""
+def embedding_gather(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, bad_flag: torch.Tensor | None = None,
+                     scale: float = 1.0) -> None:
+    """out[t] = table[ids[t]] * scale as float32 rows."""
     T = ids.numel()
     V, H = table.shape
     if out.shape != (T, H):
         raise KernelError(f"embedding_gather: out must be [{T}, {H}], got {list(out.shape)}")
     rc = library().cib_embedding_gather(
         _cuda(ids, "ids", torch.int32), _cuda(table, "table"), _code(table, "table"), _cuda(out, "out", torch.float32),
-        T, H, V, _cuda(bad_flag, "bad_flag", torch.int32) if bad_flag is not None else None, _stream())
+        T, H, V, _cuda(bad_flag, "bad_flag", torch.int32) if bad_flag is not None else None, float(scale), _stream())
     _check(rc, "embedding_gather")
     _count()
 
@@ -178,6 +189,55 @@ def add_rmsnorm(residual: torch.Tensor, delta: torch.Tensor | None, weight: torc
         float(eps), _cuda(out, "out") if out is not None else None, _code(out, "out") if out is not None else 0,
         rows, H, _stream())
     _check(rc, "add_rmsnorm")
+    _count()
+
+
+def sandwich_layernorm(residual: torch.Tensor, y: torch.Tensor | None, post: tuple | None, extra: torch.Tensor | None,
+                       pre: tuple | None, out: torch.Tensor | None) -> None:
+    """One pass over the 32-bit residual rows: ``residual += post-norm(y)`` (``post = (gain, bias, eps)``; a plain
+    ``+= y`` when ``post`` is None), ``residual += extra``, ``out = norm(residual)`` with ``pre = (gain, bias, eps)``.
+    Every part may be left out.  Layer norm with gain and bias, 32-bit statistics."""
+    rows, H = residual.shape
+    vecs = [v for pair in (post, pre) if pair is not None for v in pair[:2]]
+    if any(v.numel() != H for v in vecs) or len({v.dtype for v in vecs}) > 1:
+        raise KernelError(f"layernorm: gains and biases must have {H} elements and one dtype")
+    for name, t in (("y", y), ("extra", extra), ("out", out)):
+        if t is not None and t.shape != residual.shape:
+            raise KernelError(f"layernorm: {name} {list(t.shape)} does not match residual {list(residual.shape)}")
+    if post is not None and y is None:
+        raise KernelError("layernorm: an output norm needs rows to norm")
+    if out is not None and pre is None:
+        raise KernelError("layernorm: out needs the norm's gain and bias")
+    vd = _code(vecs[0], "gain") if vecs else 0
+    rc = library().cib_sandwich_layernorm(
+        _cuda(residual, "residual", torch.float32), _cuda(y, "y") if y is not None else None, _code(y, "y") if y is not None else 0,
+        _cuda(post[0], "post gain") if post else None, _cuda(post[1], "post bias") if post else None, float(post[2]) if post else 0.0,
+        _cuda(extra, "extra", torch.float32) if extra is not None else None,
+        _cuda(pre[0], "gain") if pre else None, _cuda(pre[1], "bias") if pre else None, float(pre[2]) if pre else 0.0, vd,
+        _cuda(out, "out") if out is not None else None, _code(out, "out") if out is not None else 0, rows, H, _stream())
+    _check(rc, "sandwich_layernorm")
+    _count()
+
+
+def relu_squared(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out = max(x, 0) ** 2, element by element."""
+    if out.shape != x.shape or out.dtype != x.dtype:
+        raise KernelError("relu_squared: out does not fit x")
+    rc = library().cib_relu_squared(_cuda(x, "x"), _cuda(out, "out"), _code(x, "x"), x.numel(), _stream())
+    _check(rc, "relu_squared")
+    _count()
+
+
+def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, j] = x[t, j] * sigmoid(gate[t, j]); x and gate may be column ranges of wider rows."""
+    rows, cols = x.shape
+    if gate.shape != x.shape or out.shape != x.shape or not (x.dtype == gate.dtype == out.dtype):
+        raise KernelError("sigmoid_gate: x, gate and out must have one shape and dtype")
+    if x.stride(1) != 1 or gate.stride(1) != 1:
+        raise KernelError("sigmoid_gate: rows must be dense")
+    rc = library().cib_sigmoid_gate(_cuda(x, "x", contiguous=False), x.stride(0), _cuda(gate, "gate", contiguous=False),
+                                    gate.stride(0), _cuda(out, "out"), _code(x, "x"), rows, cols, _stream())
+    _check(rc, "sigmoid_gate")
     _count()
 
 
@@ -260,6 +320,65 @@ def paged_attention_generic(q: torch.Tensor, out: torch.Tensor, cache: torch.Ten
         _cuda(token_request, "token_request", torch.int32), T, num_q_heads, num_kv_heads, head_dim, float(scale),
         int(window), _stream())
     _check(rc, "paged_attention_generic")
+    _count()
+
+
+def latent_prep(proj: torch.Tensor, q_off: int, rq: int, kv_off: int, rk: int, dr: int, q_gain: torch.Tensor,
+                kv_gain: torch.Tensor, eps: float, positions: torch.Tensor, freq: torch.Tensor | None, rot_dims: int,
+                slot_mapping: torch.Tensor | None, cache: torch.Tensor | None, cq_out: torch.Tensor) -> None:
+    """Per token of the stacked down-projection rows ``proj``: RMS norm of the query latent (columns q_off..+rq) into
+    ``cq_out``; RMS norm of the key/value latent (kv_off..+rk) and interleaved rotary encoding of the ``dr`` columns
+    after it, both written to the token's slot of ``cache[page, 0, 0, slot, rk + dr]`` (if a cache is given)."""
+    T, stride = proj.shape
+    if proj.stride(1) != 1 or cq_out.shape != (T, rq) or cq_out.dtype != proj.dtype or cq_out.stride(1) != 1:
+        raise KernelError("latent_prep: rows do not fit")
+    if q_gain.numel() != rq or kv_gain.numel() != rk or q_gain.dtype != kv_gain.dtype:
+        raise KernelError("latent_prep: gains do not fit the latents")
+    slots = 0
+    if cache is not None:
+        if cache.dim() != 5 or tuple(cache.shape[1:3]) != (1, 1) or cache.shape[4] != rk + dr or cache.dtype != proj.dtype:
+            raise KernelError(f"latent_prep: cache must be [pages, 1, 1, page_size, {rk + dr}] of the rows' dtype, got {list(cache.shape)}")
+        if slot_mapping is None:
+            raise KernelError("latent_prep: a cache write needs slot_mapping")
+        slots = cache.shape[0] * cache.shape[3]
+    rc = library().cib_latent_prep(
+        _cuda(proj, "proj", contiguous=False), _code(proj, "proj"), proj.stride(0), q_off, rq, kv_off, rk, dr,
+        _cuda(q_gain, "q_gain"), _cuda(kv_gain, "kv_gain"), _code(q_gain, "q_gain"), float(eps),
+        _cuda(positions, "positions", torch.int32), _cuda(freq, "freq", torch.float32) if freq is not None else None,
+        rot_dims if freq is not None else 0, _cuda(slot_mapping, "slot_mapping", torch.int32) if cache is not None else None,
+        _cuda(cache, "cache") if cache is not None else None, slots, _cuda(cq_out, "cq_out", contiguous=False),
+        cq_out.stride(0), T, _stream())
+    _check(rc, "latent_prep")
+    _count()
+
+
+def latent_attention_generic(q_abs: torch.Tensor, q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor,
+                             block_table: torch.Tensor, query_start_loc: torch.Tensor, seq_lens: torch.Tensor,
+                             token_request: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor | None, rot_dims: int,
+                             sinks: torch.Tensor | None, num_heads: int, dn: int, rk: int, dr: int, scale: float,
+                             window: int = 0) -> None:
+    """Causal multi-query attention over cached latent rows ``[c | k_rot]``: ``q_abs[T, H*rk]`` are the queries with the
+    key up-projection folded in, ``q[T, H*(dn+dr)]`` holds each head's rotary part (encoded by the kernel), ``out[T, H*rk]``
+    the weighted sums of the latents.  ``sinks[H]``: per-head scores that only join the softmax denominator."""
+    T = q.shape[0]
+    if q_abs.shape != (T, num_heads * rk) or out.shape != (T, num_heads * rk) or q.shape[1] != num_heads * (dn + dr):
+        raise KernelError("latent_attention: q_abs / q / out do not fit the sizes")
+    if q_abs.stride(1) != 1 or q.stride(1) != 1 or out.stride(1) != 1 or out.dtype != q.dtype or cache.dtype != q.dtype:
+        raise KernelError("latent_attention: rows must be dense and of one dtype")
+    if cache.dim() != 5 or tuple(cache.shape[1:3]) != (1, 1) or cache.shape[4] != rk + dr:
+        raise KernelError(f"latent_attention: cache must be [pages, 1, 1, page_size, {rk + dr}], got {list(cache.shape)}")
+    if sinks is not None and sinks.numel() != num_heads:
+        raise KernelError("latent_attention: one sink per head")
+    rc = library().cib_latent_attention_generic(
+        _cuda(q_abs, "q_abs", contiguous=False), _code(q_abs, "q_abs"), q_abs.stride(0), _cuda(q, "q", contiguous=False),
+        _code(q, "q"), q.stride(0), dn, _cuda(out, "out", contiguous=False), out.stride(0), _cuda(cache, "cache"),
+        cache.shape[0], cache.shape[3], _cuda(block_table, "block_table", torch.int32), block_table.stride(0),
+        _cuda(query_start_loc, "query_start_loc", torch.int32), _cuda(seq_lens, "seq_lens", torch.int32),
+        _cuda(token_request, "token_request", torch.int32), _cuda(positions, "positions", torch.int32),
+        _cuda(freq, "freq", torch.float32) if freq is not None else None, rot_dims if freq is not None else 0,
+        _cuda(sinks, "sinks") if sinks is not None else None, _code(sinks, "sinks") if sinks is not None else 0,
+        T, num_heads, rk, dr, float(scale), int(window), _stream())
+    _check(rc, "latent_attention_generic")
     _count()
 
 
@@ -430,6 +549,49 @@ def gemm_generic(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
         _cuda(a, "a", contiguous=False), a.stride(0), _cuda(w, "w", contiguous=False), w.stride(0), _code(a, "a"),
         _cuda(out, "out", contiguous=False), out.stride(0), _code(out, "out"), M, N, K, _stream())
     _check(rc, "gemm_generic")
+    _count()
+
+
+def gemm_generic_batched(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[b, M, N] = a[b, M, K] @ w[b, N, K]^T for every b, 32-bit FMA accumulation, any sizes.  The three tensors
+    may be strided views (heads side by side inside wider rows); only their last axis must be dense."""
+    B, M, K = a.shape
+    B2, N, K2 = w.shape
+    if B != B2 or K != K2 or out.shape != (B, M, N) or a.dtype != w.dtype:
+        raise KernelError(f"gemm: a {list(a.shape)} {a.dtype}, w {list(w.shape)} {w.dtype}, out {list(out.shape)} do not fit")
+    if a.stride(2) != 1 or w.stride(2) != 1 or out.stride(2) != 1:
+        raise KernelError("gemm: rows must be dense")
+    rc = library().cib_gemm_generic_batched(
+        _cuda(a, "a", contiguous=False), a.stride(1), a.stride(0), _cuda(w, "w", contiguous=False), w.stride(1), w.stride(0),
+        _code(a, "a"), _cuda(out, "out", contiguous=False), out.stride(1), out.stride(0), _code(out, "out"), M, N, K, B, _stream())
+    _check(rc, "gemm_generic_batched")
+    _count()
+
+
+def moe_table_feed_forward(h: torch.Tensor, ids: torch.Tensor, table: torch.Tensor, gate_up: torch.Tensor,
+                           down: torch.Tensor, base: torch.Tensor | None, out: torch.Tensor) -> None:
+    """out[t] = base[t] + (1/top) * sum over k of expert(table[ids[t], k])(h[t]) with gated experts
+    ``down_e(silu(gate_e h) * up_e h)``; ``gate_up[E, 2 ff, W]`` (gate rows first), ``down[E, W, ff]``, ``table[V, top]``.
+    Two launches (a matrix-vector product per token and choice)."""
+    T, W = h.shape
+    E, two_ff, W2 = gate_up.shape
+    ff = two_ff // 2
+    V, top = table.shape
+    if W2 != W or down.shape != (E, W, ff) or out.shape != (T, W) or not (h.dtype == gate_up.dtype == down.dtype == out.dtype):
+        raise KernelError("moe_table: weights, rows and out do not fit")
+    if h.stride(1) != 1 or (base is not None and (base.shape != (T, W) or base.stride(1) != 1 or base.dtype != h.dtype)):
+        raise KernelError("moe_table: rows must be dense and of one dtype")
+    act = torch.empty((T, top, ff), dtype=h.dtype, device=h.device)
+    lib = library()
+    rc = lib.cib_moe_table_gate_up(_cuda(h, "h", contiguous=False), h.stride(0), _code(h, "h"), _cuda(ids, "ids", torch.int32),
+                                   _cuda(table, "table", torch.int32), V, top, E, _cuda(gate_up, "gate_up"), _cuda(act, "act"),
+                                   T, W, ff, _stream())
+    _check(rc, "moe_table_gate_up")
+    rc = lib.cib_moe_table_down(_cuda(act, "act"), _code(act, "act"), _cuda(ids, "ids", torch.int32), _cuda(table, "table", torch.int32),
+                                V, top, E, _cuda(down, "down"), _cuda(base, "base", contiguous=False) if base is not None else None,
+                                base.stride(0) if base is not None else 0, 1.0 / top, _cuda(out, "out"), T, W, ff, _stream())
+    _check(rc, "moe_table_down")
+    _count()
     _count()
 
 

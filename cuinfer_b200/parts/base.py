@@ -28,15 +28,35 @@ class ResidualStream:
     """The 32-bit residual rows of a step and a delta that has not been added yet.
 
     Keeping the last sub-layer's output pending lets the next norm do the add, the store of the new
-    residual and the normalisation in one pass.
+    residual and the normalisation in one pass.  Two more things may be outstanding: ``pending_norm``, a norm that the
+    pending rows go through BEFORE they are added (a layer that norms a sub-layer's output), and ``extra``, 32-bit
+    rows that are added as well (a model that feeds its embedding output in again).  A norm that can do all of it in
+    its own pass does; anything else calls ``settle()`` first, after which only ``residual`` counts.
     """
 
-    __slots__ = ("residual", "pending", "_spare")
+    __slots__ = ("residual", "pending", "pending_norm", "extra", "_spare")
 
     def __init__(self, residual: torch.Tensor, pending: Optional[torch.Tensor] = None) -> None:
         self.residual = residual
         self.pending = pending
+        self.pending_norm: Optional["Norm"] = None
+        self.extra: Optional[torch.Tensor] = None
         self._spare: Optional[torch.Tensor] = None
+
+    @property
+    def plain(self) -> bool:
+        """True when what is outstanding is at most a plain delta (``pending``) to be added as it is."""
+        return self.pending_norm is None and self.extra is None
+
+    def settle(self) -> None:
+        """Fold a normed delta and extra rows into the residual.  A plain pending delta stays pending: every norm and
+        the gather of the wanted rows add it themselves."""
+        if self.pending_norm is not None:
+            self.pending_norm.fold(self)
+        if self.extra is not None:
+            from .. import kernels
+            kernels.sandwich_layernorm(self.residual, None, None, self.extra, None, None)
+            self.extra = None
 
     def spare(self) -> torch.Tensor:
         """A second buffer of the residual's shape, for kernels that write the new residual beside the old."""
@@ -118,6 +138,11 @@ class Norm(Part):
 
     def norm_rows(self, rows: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
+
+    def fold(self, stream: ResidualStream) -> None:
+        """``stream.residual += self(stream.pending)`` (and ``stream.extra``, if the norm can add it in the same pass);
+        nothing is pending afterwards.  Only a norm that a block uses on a sub-layer's OUTPUT needs this."""
+        raise NotImplementedError(f"{type(self).__name__} cannot norm a sub-layer's output")
 
     def fusable_rms(self) -> Optional[tuple]:
         """``(gain, eps)`` if this norm is exactly ``x * rsqrt(mean(x^2) + eps) * gain`` over the whole row, so that a

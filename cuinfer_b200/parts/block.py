@@ -41,3 +41,38 @@ class PreNormBlock(Block):
         if getattr(consumer, "accepts_lazy_norm", False):
             return LazyNorm(stream, norm)
         return norm.add_norm(stream)
+
+
+@BLOCKS.register("sandwich")
+class SandwichBlock(Block):
+    """``x += post1(mixer(pre1(x))); x += post2(feed_forward(pre2(x)))``: every sub-layer has a norm on its input and
+    another on its output.  Spec: ``PartSpec("sandwich", norm_names=(pre1, post1, pre2, post2))``.  A layer whose
+    feed-forward is of kind ``none`` has the first two norms only.
+
+    A sub-layer's output stays pending together with its output norm (``stream.pending_norm``); the next input norm —
+    this layer's or the next layer's — applies that norm, adds, stores the residual and norms again in one kernel."""
+
+    def __init__(self, spec: PartSpec, *, mixer: Mixer, feed_forward: FeedForward,
+                 make_norm: Callable[[str], Norm], prefix: str) -> None:
+        super().__init__(spec, mixer=mixer, feed_forward=feed_forward, make_norm=make_norm, prefix=prefix)
+        pre1, post1, pre2, post2 = spec.get("norm_names", ("norm1", "norm1b", "norm2", "norm2b"))
+        self.mixer_norm = make_norm(f"{prefix}.{pre1}")
+        self.mixer_out_norm = make_norm(f"{prefix}.{post1}")
+        self.has_feed_forward = not getattr(feed_forward, "absent", False)
+        self.feed_forward_norm = make_norm(f"{prefix}.{pre2}") if self.has_feed_forward else None
+        self.feed_forward_out_norm = make_norm(f"{prefix}.{post2}") if self.has_feed_forward else None
+
+    def parts(self) -> List[Part]:
+        out: List[Part] = [self.mixer_norm, self.mixer, self.mixer_out_norm]
+        if self.has_feed_forward:
+            out += [self.feed_forward_norm, self.feed_forward, self.feed_forward_out_norm]
+        return out
+
+    def forward(self, stream: ResidualStream, ctx: StepContext, run: int) -> None:
+        h = self.mixer_norm.add_norm(stream)
+        stream.pending = self.mixer.forward(h, ctx, run)
+        stream.pending_norm = self.mixer_out_norm
+        if self.has_feed_forward:
+            h = self.feed_forward_norm.add_norm(stream)
+            stream.pending = self.feed_forward.forward(h, ctx)
+            stream.pending_norm = self.feed_forward_out_norm

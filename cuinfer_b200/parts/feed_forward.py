@@ -50,3 +50,119 @@ class SwiGLU(FeedForward):
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         act = self.gate_up.forward(x, silu_pair=True)       # silu(gate) * up, fused where the kernel allows
         return self.down.forward(act)
+
+
+@FEED_FORWARDS.register("none")
+class NoFeedForward(FeedForward):
+    """A layer without a feed-forward sub-layer; a block that sees ``absent`` leaves the sub-layer and its norms out."""
+
+    absent = True
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        raise RuntimeError("a layer without feed-forward has nothing to run")
+
+
+@FEED_FORWARDS.register("relu2")
+class SquaredReluFeedForward(FeedForward):
+    """``down( relu(up(x)) ** 2 )``, no gate, no biases.  Spec: ``PartSpec("relu2", intermediate_size=I,
+    names=(up, down))`` with tensor names relative to the part's prefix."""
+
+    def __init__(self, spec: PartSpec, *, hidden_size: int, prefix: str, dtype: torch.dtype) -> None:
+        super().__init__(spec, hidden_size=hidden_size, prefix=prefix, dtype=dtype)
+        self.intermediate_size = int(spec.intermediate_size)
+        up, down = spec.get("names", ("up_proj.weight", "down_proj.weight"))
+        self.up = Linear([f"{prefix}.{up}"], [self.intermediate_size], hidden_size, dtype)
+        self.down = Linear([f"{prefix}.{down}"], [hidden_size], self.intermediate_size, dtype)
+
+    def tensors(self) -> List[TensorSpec]:
+        return self.up.tensors() + self.down.tensors()
+
+    def load(self, store) -> None:
+        self.up.load(store)
+        self.down.load(store)
+        self.up.warm_next = self.down.weight
+
+    def first_weight(self) -> Optional[torch.Tensor]:
+        return self.up.weight
+
+    def warm_after(self, weight: Optional[torch.Tensor]) -> None:
+        self.down.warm_next = weight
+
+    def workspace_bytes(self, tokens: int) -> int:
+        return 2 * self.up.workspace_bytes(tokens) + self.down.workspace_bytes(tokens)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        y = self.up.forward(x)
+        act = torch.empty_like(y)
+        kernels.relu_squared(y, act)
+        return self.down.forward(act)
+
+
+@FEED_FORWARDS.register("moe_table")
+class TableRoutedExperts(FeedForward):
+    """A mixture of SiLU-gated experts without a router: an integer table ``[vocab, top]`` names, for every token id,
+    the ``top`` experts of a token carrying that id; each has weight ``1 / top``.  An optional shared expert of the same
+    form (size ``shared_size``) runs for every token and is added.
+
+    Spec: ``PartSpec("moe_table", experts=E, top=k, intermediate_size=I, vocab_size=V, shared_size=S or 0,
+    expert_names="e{}.gate|e{}.up|e{}.down", table_name="table", shared_names=("shared.gate", "shared.up", "shared.down"))``.
+    The experts' matrices are stacked at load: gate and up rows of expert e side by side in ``[E, 2I, H]``, down in
+    ``[E, H, I]``."""
+
+    def __init__(self, spec: PartSpec, *, hidden_size: int, prefix: str, dtype: torch.dtype) -> None:
+        super().__init__(spec, hidden_size=hidden_size, prefix=prefix, dtype=dtype)
+        self.experts = int(spec.experts)
+        self.top = int(spec.top)
+        self.intermediate_size = int(spec.intermediate_size)
+        self.vocab_size = int(spec.vocab_size)
+        self.shared_size = int(spec.get("shared_size", 0) or 0)
+        if not 0 < self.top <= self.experts:
+            raise ValueError(f"moe_table: top={self.top} of {self.experts} experts")
+        gate, up, down = spec.get("expert_names", ("e{}.gate", "e{}.up", "e{}.down"))
+        p = prefix
+        self._gate_up_specs = [TensorSpec(f"{p}.{n.format(e)}", (self.intermediate_size, hidden_size))
+                               for e in range(self.experts) for n in (gate, up)]
+        self._down_specs = [TensorSpec(f"{p}.{down.format(e)}", (hidden_size, self.intermediate_size)) for e in range(self.experts)]
+        self._table_spec = TensorSpec(f"{p}.{spec.get('table_name', 'table')}", (self.vocab_size, self.top), integer=True,
+                                      modulus=self.experts)
+        self.shared: Optional[SwiGLU] = None
+        if self.shared_size:
+            sg, su, sd = spec.get("shared_names", ("shared.gate", "shared.up", "shared.down"))
+            self.shared_gate_up = Linear([f"{p}.{sg}", f"{p}.{su}"], [self.shared_size, self.shared_size], hidden_size, dtype)
+            self.shared_down = Linear([f"{p}.{sd}"], [hidden_size], self.shared_size, dtype)
+        self.gate_up: Optional[torch.Tensor] = None
+        self.down: Optional[torch.Tensor] = None
+        self.table: Optional[torch.Tensor] = None
+
+    def tensors(self) -> List[TensorSpec]:
+        out = self._gate_up_specs + self._down_specs + [self._table_spec]
+        if self.shared_size:
+            out += self.shared_gate_up.tensors() + self.shared_down.tensors()
+        return out
+
+    def load(self, store) -> None:
+        E, I, H = self.experts, self.intermediate_size, self.hidden_size
+        self.gate_up = store.get_stacked(self._gate_up_specs).to(self.dtype).view(E, 2 * I, H)
+        self.down = store.get_stacked(self._down_specs).to(self.dtype).view(E, H, I)
+        self.table = store.get(self._table_spec).to(torch.int32).contiguous()
+        if self.shared_size:
+            self.shared_gate_up.load(store)
+            self.shared_down.load(store)
+
+    def first_weight(self) -> Optional[torch.Tensor]:
+        return self.shared_gate_up.weight if self.shared_size else None
+
+    def workspace_bytes(self, tokens: int) -> int:
+        width = 2 if self.dtype == torch.bfloat16 else 4
+        own = tokens * (self.top * self.intermediate_size + self.hidden_size) * width
+        if self.shared_size:
+            own += self.shared_gate_up.workspace_bytes(tokens, silu_pair=True) + self.shared_down.workspace_bytes(tokens)
+        return own
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        base = None
+        if self.shared_size:
+            base = self.shared_down.forward(self.shared_gate_up.forward(x, silu_pair=True))
+        out = torch.empty((x.shape[0], self.hidden_size), dtype=x.dtype, device=x.device)
+        kernels.moe_table_feed_forward(x, ctx.token_ids, self.table, self.gate_up, self.down, base, out)
+        return out

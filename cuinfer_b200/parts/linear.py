@@ -122,7 +122,7 @@ class Linear:
         if lazy and x._rows is None:
             stream = x.stream
             rms = x.norm.fusable_rms()
-            if (rms is not None and stream.residual.is_contiguous()
+            if (rms is not None and stream.plain and stream.residual.is_contiguous()
                     and K <= gemm_dispatch.FUSED_NORM_MAX_K and kernels.gemm_skinny_supports(M, N, K, True)
                     and (stream.pending is None or stream.pending.is_contiguous())):
                 out = torch.empty((M, out_cols), dtype=out_dtype, device=w.device)

@@ -109,7 +109,7 @@ class DecoderModel:
                 continue
             if run in self.cache_source:
                 src_need = self.blocks[self.order[self.cache_source[run]]].mixer.cache_need()
-                if src_need is None or (src_need.num_kv_heads, src_need.head_dim) != (need.num_kv_heads, need.head_dim):
+                if src_need is None or (src_need.num_kv_heads, src_need.head_dim, src_need.planes) != (need.num_kv_heads, need.head_dim, need.planes):
                     raise ValueError(f"run {run} cannot read run {self.cache_source[run]}'s cache: shapes differ")
                 continue
             out[run] = need
@@ -133,22 +133,35 @@ class DecoderModel:
         """Device memory a step of ``tokens`` rows with ``rows`` wanted logits needs beside weights and cache: the
         32-bit residual stream with its spare and a pending delta, the widest block's intermediate results, and the
         wanted rows with their logits (twice: the sampler works on a copy)."""
-        residual = 3 * tokens * self.hidden_size * 4
+        residual = (4 if self.spec.reinject_embedding_before else 3) * tokens * self.hidden_size * 4
         widest = max((block.workspace_bytes(tokens) for block in self.blocks), default=0)
         head = rows * (self.hidden_size * 8 + self.vocab_size * 8)
         return residual + widest + head
 
     # ---- compute -------------------------------------------------------------------------------------
-    def forward(self, ctx: StepContext) -> ResidualStream:
+    def forward(self, ctx: StepContext, tap=None) -> ResidualStream:
+        """``tap(run, stream)``, if given, is called after every layer run with everything folded into the residual
+        (``stream.residual`` plus a plain ``stream.pending``, if any, is the stream after that run)."""
         residual = torch.empty((ctx.num_tokens, self.hidden_size), dtype=torch.float32, device=ctx.token_ids.device)
-        kernels.embedding_gather(ctx.token_ids, self.embedding, residual, self._bad_id_flag)
+        kernels.embedding_gather(ctx.token_ids, self.embedding, residual, self._bad_id_flag, self.spec.embedding_scale)
         stream = ResidualStream(residual)
+        # a model that feeds its embedding output in again keeps a copy: the residual rows are updated in place
+        again = set(self.spec.reinject_embedding_before)
+        embedded = residual.clone() if again else None
         for run, layer in self.runs():
+            if run in again:
+                if stream.extra is not None:
+                    stream.settle()
+                stream.extra = embedded
             self.blocks[layer].forward(stream, ctx, run)
+            if tap is not None:
+                stream.settle()
+                tap(run, stream)
         return stream
 
     def logits(self, stream: ResidualStream, indices: torch.Tensor) -> torch.Tensor:
         """32-bit logits ``[len(indices), vocab]`` of the rows ``indices`` of the step."""
+        stream.settle()
         rows = torch.empty((indices.numel(), self.hidden_size), dtype=torch.float32, device=indices.device)
         kernels.gather_rows(stream.residual, stream.pending, indices, rows)
         normed = self.final_norm.norm_rows(rows)

@@ -31,6 +31,7 @@ class RMSNorm(Norm):
         return (self.weight, self.eps) if self.weight is not None else None
 
     def add_norm(self, stream: ResidualStream) -> torch.Tensor:
+        stream.settle()
         out = torch.empty(stream.residual.shape, dtype=self.dtype, device=stream.residual.device)
         kernels.add_rmsnorm(stream.residual, stream.pending, self.weight, self.eps, out)
         stream.pending = None
@@ -39,4 +40,62 @@ class RMSNorm(Norm):
     def norm_rows(self, rows: torch.Tensor) -> torch.Tensor:
         out = torch.empty(rows.shape, dtype=self.dtype, device=rows.device)
         kernels.add_rmsnorm(rows, None, self.weight, self.eps, out)
+        return out
+
+
+@NORMS.register("layernorm")
+class LayerNorm(Norm):
+    """``(x - mean) / sqrt(var + eps) * gain + bias`` over the row, ``var`` the mean of the squared deviations, all in
+    32 bits with one rounding at the end.  Spec: ``PartSpec("layernorm", eps=..., weight_suffix=".weight",
+    bias_suffix=".bias")``: the tensors are ``prefix + suffix``.
+
+    It serves on both sides of a sub-layer.  As the norm of a sub-layer's input (``add_norm``) it folds whatever the
+    stream has outstanding — a delta that still has to go through ANOTHER layer norm (``stream.pending_norm``), extra
+    rows — into the residual in the same kernel.  As the norm of a sub-layer's output it is that ``pending_norm``;
+    ``fold`` applies it alone."""
+
+    def __init__(self, spec: PartSpec, *, hidden_size: int, prefix: str, dtype: torch.dtype) -> None:
+        super().__init__(spec, hidden_size=hidden_size, prefix=prefix, dtype=dtype)
+        self.eps = float(spec.eps)
+        self.weight: torch.Tensor | None = None
+        self.bias: torch.Tensor | None = None
+
+    def tensors(self) -> List[TensorSpec]:
+        return [TensorSpec(self.prefix + self.spec.get("weight_suffix", ".weight"), (self.hidden_size,),
+                           keep_stored_precision=True, init="ones"),
+                TensorSpec(self.prefix + self.spec.get("bias_suffix", ".bias"), (self.hidden_size,),
+                           keep_stored_precision=True, init="zeros")]
+
+    def load(self, store) -> None:
+        w, b = self.tensors()
+        self.weight, self.bias = store.get(w), store.get(b)
+        if self.weight.dtype != self.bias.dtype:
+            self.weight, self.bias = self.weight.float(), self.bias.float()
+
+    def _triple(self):
+        return (self.weight, self.bias, self.eps)
+
+    def _post_of(self, stream: ResidualStream):
+        post = stream.pending_norm
+        if post is None:
+            return None
+        if not isinstance(post, LayerNorm) or post.weight.dtype != self.weight.dtype:
+            stream.settle()                       # another kind of norm on the delta: it folds itself
+            return None
+        return post._triple()
+
+    def add_norm(self, stream: ResidualStream) -> torch.Tensor:
+        post = self._post_of(stream)
+        out = torch.empty(stream.residual.shape, dtype=self.dtype, device=stream.residual.device)
+        kernels.sandwich_layernorm(stream.residual, stream.pending, post, stream.extra, self._triple(), out)
+        stream.pending = stream.pending_norm = stream.extra = None
+        return out
+
+    def fold(self, stream: ResidualStream) -> None:
+        kernels.sandwich_layernorm(stream.residual, stream.pending, self._triple(), stream.extra, None, None)
+        stream.pending = stream.pending_norm = stream.extra = None
+
+    def norm_rows(self, rows: torch.Tensor) -> torch.Tensor:
+        out = torch.empty(rows.shape, dtype=self.dtype, device=rows.device)
+        kernels.sandwich_layernorm(rows, None, None, None, self._triple(), out)
         return out

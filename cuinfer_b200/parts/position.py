@@ -60,3 +60,40 @@ class NoPosition(PositionEncoding):
 
     def table(self) -> Optional[torch.Tensor]:
         return None
+
+
+@POSITION_ENCODINGS.register("rope_interleaved")
+class RotaryInterleaved(PositionEncoding):
+    """Rotary encoding with neighbouring pairs: over the first ``rotary_dim`` elements of the vector it is applied to,
+    element 2i pairs with 2i+1 and the pair (u, v) at position p becomes ``(u cos a - v sin a, v cos a + u sin a)`` with
+    ``a = p * f_i``, ``f_i = theta ** (-2i / rotary_dim)``.  There is no table and hence no largest position: the
+    kernels that apply it take the frequencies (32-bit, rounded once from double precision) and compute the angle and
+    its full-range sine and cosine in 32 bits.  Spec: ``PartSpec("rope_interleaved", theta=..., rotary_dim=...)``."""
+
+    def __init__(self, spec: PartSpec, *, hidden_size: int, prefix: str, dtype: torch.dtype) -> None:
+        super().__init__(spec, hidden_size=hidden_size, prefix=prefix, dtype=dtype)
+        self.theta = float(spec.theta)
+        self.rotary_dim = int(spec.rotary_dim)
+        if self.rotary_dim < 0 or self.rotary_dim % 2 or not self.theta > 0:
+            raise ValueError(f"rope_interleaved: rotary_dim must be even and theta positive, got {self.rotary_dim}, {self.theta}")
+        self._freq: Optional[torch.Tensor] = None
+        self._device: Optional[torch.device] = None
+
+    def host_frequencies(self) -> torch.Tensor:
+        i = torch.arange(self.rotary_dim // 2, dtype=torch.float64)
+        return torch.pow(torch.tensor(self.theta, dtype=torch.float64), -2.0 * i / max(self.rotary_dim, 1)).float()
+
+    def load(self, store) -> None:
+        self._device = store.device
+
+    def frequencies(self) -> Optional[torch.Tensor]:
+        """float32 [rotary_dim / 2] on the device, or None when nothing is rotated."""
+        if self.rotary_dim == 0:
+            return None
+        if self._freq is None:
+            device = torch.device(self._device or "cuda")
+            key = ("interleaved", self.theta, self.rotary_dim, str(device))
+            if key not in _TABLES:
+                _TABLES[key] = self.host_frequencies().to(device)
+            self._freq = _TABLES[key]
+        return self._freq

@@ -95,12 +95,20 @@ class ModelSpec:
     order: tuple[int, ...] | None = None
     cache_source: Mapping[int, int] = field(default_factory=dict)
     eos_token_ids: tuple[int, ...] = ()           # sampling one of these ends a request (unless it ignores them)
+    embedding_scale: float = 1.0                  # the embedding rows are multiplied by this as they enter the residual stream
+    # positions in ``order`` before which the embedding output (the residual stream as it was before the first layer)
+    # is added to the stream once more: a model that runs a span of layers several times feeds its input in again
+    # at the start of every further pass
+    reinject_embedding_before: tuple[int, ...] = ()
 
     def run_order(self) -> tuple[int, ...]:
         order = self.order if self.order is not None else tuple(range(len(self.layers)))
         for idx in order:
             if not 0 <= idx < len(self.layers):
                 raise ValueError(f"order names layer {idx}, but the model has {len(self.layers)} layers")
+        for run in self.reinject_embedding_before:
+            if not 0 < run < len(order):
+                raise ValueError(f"reinject_embedding_before names run {run}, but runs 1..{len(order) - 1} exist")
         for run, src in self.cache_source.items():
             if not (0 <= src < run < len(order)):
                 raise ValueError(f"cache_source[{run}]={src}: a run may only read the cache of an earlier run")
@@ -122,7 +130,8 @@ class TensorSpec:
     shape: tuple[int, ...]
     keep_stored_precision: bool = False
     integer: bool = False    # an integer table (kept as int32); a floating tensor in its place is refused, and vice versa
-    init: str = "normal"     # how the random-weights mode fills it: "normal" or "ones" (a gain)
+    init: str = "normal"     # how the random-weights mode fills it: "normal", "ones" (a gain), "zeros" (a bias)
+    modulus: int = 0         # for an integer table: entries are drawn from 0..modulus-1, different within a row
 
 
 @dataclass(frozen=True)
@@ -130,12 +139,14 @@ class PagedCacheNeed:
     """What a mixer keeps per token: keys and values of ``num_kv_heads`` × ``head_dim``.
 
     ``window``: None keeps every token; ``w`` keeps only the last ``w`` (pages that a request's
-    next query can no longer see are given back).
+    next query can no longer see are given back).  ``planes``: how many rows of ``head_dim`` a head keeps per
+    token — 2 for keys and values, 1 for a mixer that derives both from one cached row (a latent).
     """
 
     num_kv_heads: int
     head_dim: int
     window: int | None = None
+    planes: int = 2
 
 
 @dataclass(frozen=True)

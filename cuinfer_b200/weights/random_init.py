@@ -64,9 +64,20 @@ def counter_normal(key: int, count: int, mean: float, std: float, factor: float 
     return t.to(torch.bfloat16).float() if via_bf16 else t
 
 
+def integer_table(spec: TensorSpec, seed: int) -> torch.Tensor:
+    """An integer table ``[rows, n]`` with entries in ``0..modulus-1`` that differ within a row: row r holds
+    ``(mix(r) + k) mod modulus`` for k = 0..n-1."""
+    if len(spec.shape) != 2 or not 0 < spec.shape[1] <= spec.modulus:
+        raise ValueError(f"cannot draw the integer table '{spec.name}' of shape {list(spec.shape)} from 0..{spec.modulus - 1}")
+    rows = np.arange(spec.shape[0], dtype=np.uint64)
+    start = _splitmix64(rows + np.uint64(_tensor_seed(seed, spec.name) & 0xFFFFFFFF)) % np.uint64(spec.modulus)
+    table = (start[:, None] + np.arange(spec.shape[1], dtype=np.uint64)[None, :]) % np.uint64(spec.modulus)
+    return torch.from_numpy(table.astype(np.int32))
+
+
 def _draw_plan(spec: TensorSpec, std: float, gain_std: float, gains: Optional[Mapping[str, float]]):
     """(mean, std, factor) of a tensor: matrices N(0, std), gains 1 + N(0, gain_std), then the factors of ``gains``."""
-    mean, dev = (1.0, gain_std) if spec.init == "ones" else (0.0, std)
+    mean, dev = (1.0, gain_std) if spec.init == "ones" else (0.0, gain_std) if spec.init == "zeros" else (0.0, std)
     factor = 1.0
     for pattern, f in (gains or {}).items():
         if pattern in spec.name:
@@ -93,6 +104,9 @@ def random_tensors(config: Mapping[str, Any], seed: int, *, std: float = 0.02, g
         raise ValueError("generator must be 'torch' or 'counter'")
     out: Dict[str, torch.Tensor] = {}
     for spec in model.tensors():
+        if spec.integer:
+            out[spec.name] = integer_table(spec, seed)
+            continue
         if generator == "counter":
             mean, dev, factor = _draw_plan(spec, std, gain_std, gains)
             count = int(np.prod(spec.shape)) if spec.shape else 1
@@ -100,8 +114,8 @@ def random_tensors(config: Mapping[str, Any], seed: int, *, std: float = 0.02, g
             out[spec.name] = t.reshape(spec.shape).to(_TORCH_DTYPES[dtype])
             continue
         gen = torch.Generator().manual_seed(_tensor_seed(seed, spec.name))
-        if spec.init == "ones":
-            t = torch.ones(spec.shape, dtype=torch.float32)
+        if spec.init in ("ones", "zeros"):
+            t = torch.full(spec.shape, 1.0 if spec.init == "ones" else 0.0, dtype=torch.float32)
             if gain_std > 0:
                 t += torch.randn(spec.shape, generator=gen, dtype=torch.float32) * gain_std
         else:
@@ -176,7 +190,7 @@ class DeviceRandomStore:
         from .. import kernels
 
         if spec.integer:
-            raise WeightError(f"'{spec.name}' is an integer table; random weights are floating tensors only")
+            return integer_table(spec, self.seed).to(self.device)
         if self.dtype == torch.float32 or (spec.keep_stored_precision and self.stored == "float32"):
             target = torch.float32
         else:
