@@ -1,0 +1,376 @@
+// Attention over cached latent rows [c (rk) | k_rot (dr)] on the tensor cores (mma.sync m16n8k16, bfloat16 operands,
+// 32-bit accumulation), for prompt portions, mixed batches and decode steps alike.  What it computes is stated at
+// the head of attention_latent.cu; this file is the bfloat16 path for rk and dr that are multiples of 16, rk <= 512.
+//
+// All heads read the same rows, so a CTA's 64-row query tile is (tokens x heads) of ONE request: HB = 2^k heads side
+// by side (k smallest with HB >= min(H, 64)) times 64 / HB consecutive tokens; a decode step's single token fills the
+// tile with its heads.  Keys come in tiles of 32 rows through two cp.async stages; S = Q K^T runs over all rk + dr
+// columns, O += P V over the first rk columns of the same shared-memory tile (the values ARE the latents).  A warp owns
+// 16 rows; for rk > 256 eight warps share them in pairs, each computing S again and keeping half of the value columns
+// (128 accumulator registers a thread).  The query's rotary part is encoded as the tile is loaded; softmax statistics
+// are 32-bit in the log2 domain; the sink starts a row's running maximum and counts once in its sum.
+//
+// gridDim.z > 1 splits a tile's keys over CTAs (decode steps: few rows, long contexts).  Each split then writes its
+// running maximum, its sum and its unnormalised rows to a scratch buffer and a second kernel merges them with the sink.
+#include "common.cuh"
+#include "mma_utils.cuh"
+
+namespace cib {
+
+constexpr int kLmM = 64;       // query rows of a tile
+constexpr int kLmN = 32;       // keys of a tile
+constexpr float kLog2e = 1.4426950408889634f;
+
+template <int RKH, int CS>
+__global__ void __launch_bounds__(128 * CS)
+latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_abs, int qa_stride, const __nv_bfloat16* __restrict__ q,
+                            int q_stride, int dn, __nv_bfloat16* __restrict__ out, int out_stride, float* __restrict__ part,
+                            const __nv_bfloat16* __restrict__ cache, int num_pages, int page_size,
+                            const int* __restrict__ block_table, int table_stride, const int* __restrict__ query_start_loc,
+                            const int* __restrict__ seq_lens, int num_requests, const float* __restrict__ freq, int rot_dims,
+                            const float* __restrict__ sinks, int H, int hb_log2, int rk, int dr, float scale_log2) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __shared__ int s_req, s_tile;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int rg = warp & 3, ch = warp >> 2;               // row group of 16 rows; which half of the value columns
+    const int qrow = lane >> 2, quad = lane & 3;
+    const int D = rk + dr, LD = D + 8;                     // rows 16 bytes longer than D: ldmatrix hits every bank once
+    const int HB = 1 << hb_log2, TM = kLmM >> hb_log2;
+    const int splits = gridDim.z, split = blockIdx.z;
+
+    if (tid == 0) {
+        int t = blockIdx.x, r = 0;
+        for (; r < num_requests; ++r) {
+            const int tiles = (query_start_loc[r + 1] - query_start_loc[r] + TM - 1) / TM;
+            if (t < tiles) break;
+            t -= tiles;
+        }
+        s_req = r;
+        s_tile = t;
+    }
+    __syncthreads();
+    const int r = s_req;
+    if (r >= num_requests) return;
+    const int q0 = query_start_loc[r];
+    const int n = query_start_loc[r + 1] - q0;
+    const int seq_len = seq_lens[r];
+    const int tok0 = s_tile * TM;
+    const int head0 = blockIdx.y * HB;
+    const int* table = block_table + (size_t)r * table_stride;
+
+    __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+    __nv_bfloat16* sK = sQ + (size_t)kLmM * LD;
+    auto stage = [&](int s) { return sK + (size_t)s * kLmN * LD; };
+
+    const int k_hi = seq_len - n + min(tok0 + TM, n);      // keys < k_hi are visible to the tile's last token
+    const int tiles_all = (k_hi + kLmN - 1) / kLmN;
+    const int per = (tiles_all + splits - 1) / splits;
+    const int t_begin = split * per, t_end = min(tiles_all, t_begin + per);
+
+    auto load_keys = [&](int s, int key0) {
+        __nv_bfloat16* dst = stage(s);
+        const int chunks = D / 8;
+        for (int idx = tid; idx < kLmN * chunks; idx += blockDim.x) {
+            const int row = idx / chunks, chunk = idx % chunks;
+            const int key = key0 + row;
+            bool ok = key < k_hi;
+            int page = 0;
+            if (ok) {
+                page = table[key / page_size];
+                ok = page >= 0 && page < num_pages;
+            }
+            const __nv_bfloat16* src = cache + ((size_t)(ok ? page : 0) * page_size + (ok ? key % page_size : 0)) * D + chunk * 8;
+            cp_async16(dst + row * LD + chunk * 8, src, ok);
+        }
+    };
+
+    // ---- query tile: [Uk^T q_plain (rk) | rot(q_rot) (dr)] per (token, head) row ----
+    {
+        const int chunks = rk / 8;
+        for (int idx = tid; idx < kLmM * chunks; idx += blockDim.x) {
+            const int row = idx / chunks, chunk = idx % chunks;
+            const int tl = tok0 + (row >> hb_log2), head = head0 + (row & (HB - 1));
+            const bool ok = tl < n && head < H;
+            const __nv_bfloat16* src = q_abs + (size_t)(q0 + (ok ? tl : 0)) * qa_stride + (size_t)(ok ? head : 0) * rk + chunk * 8;
+            cp_async16(sQ + row * LD + chunk * 8, src, ok);
+        }
+        const int pairs = dr / 2;
+        for (int idx = tid; idx < kLmM * pairs; idx += blockDim.x) {
+            const int row = idx / pairs, i = idx % pairs;
+            const int tl = tok0 + (row >> hb_log2), head = head0 + (row & (HB - 1));
+            float u = 0.f, v = 0.f;
+            if (tl < n && head < H) {
+                const __nv_bfloat16* src = q + (size_t)(q0 + tl) * q_stride + (size_t)head * (dn + dr) + dn + 2 * i;
+                u = __bfloat162float(src[0]);
+                v = __bfloat162float(src[1]);
+                if (2 * i + 1 < rot_dims) {
+                    float sn, cs;
+                    sincosf((float)(seq_len - n + tl) * freq[i], &sn, &cs);
+                    const float a = u * cs - v * sn, b = v * cs + u * sn;
+                    u = a;
+                    v = b;
+                }
+            }
+            *reinterpret_cast<uint32_t*>(sQ + row * LD + rk + 2 * i) = pack_bf16(u, v);
+        }
+    }
+    if (t_begin < t_end) load_keys(0, t_begin * kLmN);
+    cp_async_commit();
+
+    int pos_row[2], head_row[2];
+    bool row_ok[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int row = rg * 16 + qrow + 8 * h;
+        const int tl = tok0 + (row >> hb_log2);
+        head_row[h] = head0 + (row & (HB - 1));
+        row_ok[h] = tl < n && head_row[h] < H;
+        pos_row[h] = row_ok[h] ? seq_len - n + tl : -1;
+    }
+    const int warp_pos_min = seq_len - n + min(tok0 + ((rg * 16) >> hb_log2), n - 1);
+
+    float o[RKH / 8][4];
+#pragma unroll
+    for (int i = 0; i < RKH / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    float m_run[2], l_run[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const bool with_sink = splits == 1 && sinks != nullptr && row_ok[h];
+        m_run[h] = with_sink ? sinks[head_row[h]] * kLog2e : -INFINITY;
+        l_run[h] = with_sink && quad == 0 ? 1.f : 0.f;
+    }
+    const int col_base = ch * RKH;                          // this warp's value columns: col_base .. col_base + RKH (< rk)
+    const int mat = lane >> 3, rr = lane & 7;
+
+    for (int t = t_begin; t < t_end; ++t) {
+        const int key0 = t * kLmN;
+        if (t + 1 < t_end) load_keys((t + 1 - t_begin) & 1, key0 + kLmN);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        const __nv_bfloat16* sKt = stage((t - t_begin) & 1);
+
+        // ---- S = Q K^T : 16 x 32 per warp, over all rk + dr columns ----
+        float s[kLmN / 8][4];
+#pragma unroll
+        for (int nt = 0; nt < kLmN / 8; ++nt) { s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f; }
+        {
+            const int arow = rg * 16 + (mat & 1) * 8 + rr;
+            const uint32_t a_base = smem_u32(sQ + arow * LD + (mat >> 1) * 8);
+            const uint32_t b_base = smem_u32(sKt + ((mat >> 1) * 8 + rr) * LD + (mat & 1) * 8);
+#pragma unroll 4
+            for (int kt = 0; kt < D / 16; ++kt) {
+                uint32_t a[4];
+                ldmatrix_x4(a, a_base + kt * 32);
+#pragma unroll
+                for (int np = 0; np < kLmN / 16; ++np) {
+                    uint32_t b[4];
+                    ldmatrix_x4(b, b_base + (np * 16 * LD + kt * 16) * 2);
+                    mma_bf16_16816(s[2 * np], a, b[0], b[1]);
+                    mma_bf16_16816(s[2 * np + 1], a, b[2], b[3]);
+                }
+            }
+        }
+        // ---- scale, causal mask where the tile touches the diagonal, running maximum ----
+        const bool need_mask = key0 + kLmN - 1 > warp_pos_min;
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nt = 0; nt < kLmN / 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int h = e >> 1;
+                float v = s[nt][e] * scale_log2;
+                if (need_mask) {
+                    const int key = key0 + nt * 8 + quad * 2 + (e & 1);
+                    v = key <= pos_row[h] ? v : -INFINITY;
+                }
+                s[nt][e] = v;
+                mx[h] = fmaxf(mx[h], v);
+            }
+        }
+        float corr[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+            const float m_new = fmaxf(m_run[h], mx[h]);
+            corr[h] = m_run[h] == -INFINITY ? 0.f : exp2f(m_run[h] - m_new);
+            m_run[h] = m_new;
+            l_run[h] *= corr[h];
+        }
+#pragma unroll
+        for (int nt = 0; nt < kLmN / 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float mref = m_run[e >> 1];
+                const float p = (s[nt][e] == -INFINITY || mref == -INFINITY) ? 0.f : exp2f(s[nt][e] - mref);
+                s[nt][e] = p;
+                l_run[e >> 1] += p;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < RKH / 8; ++i) { o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1]; }
+        // ---- O += P V, V = the tile's first rk columns ----
+#pragma unroll
+        for (int kp = 0; kp < kLmN / 16; ++kp) {
+            uint32_t pf[4];
+            pf[0] = pack_bf16(s[2 * kp][0], s[2 * kp][1]);
+            pf[1] = pack_bf16(s[2 * kp][2], s[2 * kp][3]);
+            pf[2] = pack_bf16(s[2 * kp + 1][0], s[2 * kp + 1][1]);
+            pf[3] = pack_bf16(s[2 * kp + 1][2], s[2 * kp + 1][3]);
+            const uint32_t v_base = smem_u32(sKt + (kp * 16 + (mat & 1) * 8 + rr) * LD + col_base + (mat >> 1) * 8);
+#pragma unroll
+            for (int nt = 0; nt < RKH / 16; ++nt) {
+                if (col_base + nt * 16 < rk) {                 // uniform over the warp
+                    uint32_t b[4];
+                    ldmatrix_x4_trans(b, v_base + nt * 32);
+                    mma_bf16_16816(o[2 * nt], pf, b[0], b[1]);
+                    mma_bf16_16816(o[2 * nt + 1], pf, b[2], b[3]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        float l = l_run[h];
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        if (!row_ok[h]) continue;
+        const int row = rg * 16 + qrow + 8 * h;
+        const int token = q0 + tok0 + (row >> hb_log2);
+        if (splits == 1) {
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            __nv_bfloat16* dst = out + (size_t)token * out_stride + (size_t)head_row[h] * rk;
+#pragma unroll
+            for (int i = 0; i < RKH / 8; ++i) {
+                const int col = col_base + i * 8 + quad * 2;
+                if (col < rk)
+                    *reinterpret_cast<uint32_t*>(dst + col) = pack_bf16(o[i][2 * h] * inv, o[i][2 * h + 1] * inv);
+            }
+        } else {
+            float* dst = part + (((size_t)token * H + head_row[h]) * splits + split) * (rk + 2);
+            if (ch == 0 && quad == 0) {
+                dst[0] = m_run[h];
+                dst[1] = l;
+            }
+#pragma unroll
+            for (int i = 0; i < RKH / 8; ++i) {
+                const int col = col_base + i * 8 + quad * 2;
+                if (col < rk) {
+                    dst[2 + col] = o[i][2 * h];
+                    dst[3 + col] = o[i][2 * h + 1];
+                }
+            }
+        }
+    }
+}
+
+// Merge the splits of a (token, head): M = max(sink, m_s), L = 2^(sink - M) + sum l_s 2^(m_s - M),
+// out = sum acc_s 2^(m_s - M) / L.  A warp per (token, head).
+__global__ void latent_attention_merge_kernel(const float* __restrict__ part, const float* __restrict__ sinks,
+                                              __nv_bfloat16* __restrict__ out, int out_stride, int H, int rk, int splits,
+                                              int rows) {
+    const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (w >= rows) return;
+    const int token = w / H, head = w % H;
+    const float* p = part + (size_t)w * splits * (rk + 2);
+    const float sink = sinks ? sinks[head] * kLog2e : -INFINITY;
+    float M = sink;
+    for (int s = 0; s < splits; ++s) M = fmaxf(M, p[(size_t)s * (rk + 2)]);
+    float L = sink == -INFINITY ? 0.f : exp2f(sink - M);
+    for (int s = 0; s < splits; ++s) {
+        const float m = p[(size_t)s * (rk + 2)];
+        if (m != -INFINITY) L += p[(size_t)s * (rk + 2) + 1] * exp2f(m - M);
+    }
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+    for (int c = lane; c < rk; c += 32) {
+        float acc = 0.f;
+        for (int s = 0; s < splits; ++s) {
+            const float m = p[(size_t)s * (rk + 2)];
+            if (m != -INFINITY) acc += p[(size_t)s * (rk + 2) + 2 + c] * exp2f(m - M);
+        }
+        out[(size_t)token * out_stride + (size_t)head * rk + c] = __float2bfloat16_rn(acc * inv);
+    }
+}
+
+template <int RKH, int CS>
+static int launch_latent_mma(dim3 grid, size_t smem, cudaStream_t stream, const void* q_abs, int qa_stride, const void* q,
+                             int q_stride, int dn, void* out, int out_stride, float* part, const void* cache, int num_pages,
+                             int page_size, const int* bt, int ts, const int* qsl, const int* sl, int R, const float* freq,
+                             int rot_dims, const float* sinks, int H, int hb_log2, int rk, int dr, float scale_log2) {
+    static SmemLimit limit;
+    auto kernel = latent_attention_mma_kernel<RKH, CS>;
+    if (smem > 48 * 1024 && raise_smem_limit(limit, kernel, 200 * 1024, "latent_attention_mma") != 0) return -2;
+    kernel<<<grid, 128 * CS, smem, stream>>>((const __nv_bfloat16*)q_abs, qa_stride, (const __nv_bfloat16*)q, q_stride, dn,
+                                             (__nv_bfloat16*)out, out_stride, part, (const __nv_bfloat16*)cache, num_pages,
+                                             page_size, bt, ts, qsl, sl, R, freq, rot_dims, sinks, H, hb_log2, rk, dr,
+                                             scale_log2);
+    return 0;
+}
+
+}  // namespace cib
+
+using namespace cib;
+
+extern "C" int cib_latent_attention_mma_supports(int rk, int dr, int dn) {
+    return rk > 0 && rk % 16 == 0 && rk <= 512 && dr >= 0 && dr % 16 == 0 && dn >= 0;
+}
+
+// Heads side by side in a query tile: the smallest power of two that holds min(H, 64) heads.
+static int head_block_log2(int H) {
+    int k = 0;
+    while ((1 << k) < H && k < 6) ++k;
+    return k;
+}
+
+// Row tiles a launch needs for requests of these numbers of new tokens.
+extern "C" int cib_latent_attention_mma_tiles(const int* query_lens, int num_requests, int H) {
+    const int tm = kLmM >> head_block_log2(H);
+    long long tiles = 0;
+    for (int i = 0; i < num_requests; ++i) tiles += (query_lens[i] + tm - 1) / tm;
+    return (int)(tiles > 0x7fffffff ? 0x7fffffff : tiles);
+}
+
+// `scratch`: splits > 1 needs num_tokens * H * splits * (rk + 2) floats.  `sinks` 32-bit or null.
+extern "C" int cib_latent_attention_mma(const void* q_abs, int qa_stride, const void* q, int q_stride, int dn, void* out,
+                                        int out_stride, float* scratch, const void* cache, int num_pages, int page_size,
+                                        const int* block_table, int table_stride, const int* query_start_loc,
+                                        const int* seq_lens, int num_requests, int row_tiles, const float* freq,
+                                        int rot_dims, const float* sinks, int num_tokens, int H, int rk, int dr, float scale,
+                                        int splits, cudaStream_t stream) {
+    CIB_REQUIRE(cib_latent_attention_mma_supports(rk, dr, dn), "latent_attention_mma: sizes rk=%d dr=%d are not taken", rk, dr);
+    CIB_REQUIRE(num_tokens >= 0 && H > 0 && num_requests > 0 && row_tiles >= 0, "latent_attention_mma: bad sizes");
+    CIB_REQUIRE(page_size > 0 && num_pages > 0 && table_stride > 0, "latent_attention_mma: bad cache geometry");
+    CIB_REQUIRE(rot_dims >= 0 && rot_dims <= dr && rot_dims % 2 == 0 && (rot_dims == 0 || freq), "latent_attention_mma: bad rotary part");
+    CIB_REQUIRE(qa_stride % 8 == 0 && out_stride % 2 == 0, "latent_attention_mma: rows must start on 16-byte boundaries");
+    CIB_REQUIRE(splits >= 1 && splits <= 65535 && (splits == 1 || scratch != nullptr), "latent_attention_mma: bad split");
+    if (num_tokens == 0 || row_tiles == 0) return 0;
+    const int hb_log2 = head_block_log2(H);
+    dim3 grid(row_tiles, (H + (1 << hb_log2) - 1) >> hb_log2, splits);
+    const int D = rk + dr;
+    const size_t smem = (size_t)(kLmM + 2 * kLmN) * (D + 8) * sizeof(__nv_bfloat16);
+    const float scale_log2 = scale * kLog2e;
+    int rc;
+#define CIB_LM_GO(RKH, CS)                                                                                                 \
+    rc = launch_latent_mma<RKH, CS>(grid, smem, stream, q_abs, qa_stride, q, q_stride, dn, out, out_stride, scratch, cache,  \
+                                    num_pages, page_size, block_table, table_stride, query_start_loc, seq_lens, num_requests, \
+                                    freq, rot_dims, sinks, H, hb_log2, rk, dr, scale_log2)
+    if (rk <= 32) CIB_LM_GO(32, 1);
+    else if (rk <= 64) CIB_LM_GO(64, 1);
+    else if (rk <= 128) CIB_LM_GO(128, 1);
+    else if (rk <= 256) CIB_LM_GO(256, 1);
+    else CIB_LM_GO(256, 2);
+#undef CIB_LM_GO
+    if (rc != 0) return rc;
+    CIB_LAUNCH_CHECK("latent_attention_mma");
+    if (splits > 1) {
+        const int rows = num_tokens * H;
+        latent_attention_merge_kernel<<<(rows + 3) / 4, 128, 0, stream>>>(scratch, sinks, (__nv_bfloat16*)out, out_stride, H, rk,
+                                                                           splits, rows);
+        CIB_LAUNCH_CHECK("latent_attention_merge");
+    }
+    return 0;
+}

@@ -74,6 +74,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         "cib_latent_prep": [_P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _I, _F, _P, _P, _I, _P, _P, ctypes.c_longlong, _P, _I, _I, _P],
         "cib_latent_attention_generic": [_P, _I, _I, _P, _I, _I, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _P, _P, _P, _I, _P, _I,
                                          _I, _I, _I, _I, _F, _I, _P],
+        "cib_latent_attention_mma": [_P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _P, _I, _P, _P, _I, _I, _P, _I, _P, _I, _I, _I, _I,
+                                     _F, _I, _P],
         "cib_gemm_generic_batched": [_P, _I, ctypes.c_longlong, _P, _I, ctypes.c_longlong, _I, _P, _I, ctypes.c_longlong, _I,
                                      _I, _I, _I, _I, _P],
         "cib_moe_table_gate_up": [_P, _I, _I, _P, _P, _I, _I, _I, _P, _P, _I, _I, _I, _P],
@@ -99,6 +101,10 @@ def _declare(lib: ctypes.CDLL) -> None:
         fn = getattr(lib, name)
         fn.argtypes = argtypes
         fn.restype = _I
+    lib.cib_latent_attention_mma_supports.argtypes = [_I, _I, _I]
+    lib.cib_latent_attention_mma_supports.restype = _I
+    lib.cib_latent_attention_mma_tiles.argtypes = [_P, _I, _I]
+    lib.cib_latent_attention_mma_tiles.restype = _I
     lib.cib_paged_attention_decode_supports.argtypes = [_I, _I, _I]
     lib.cib_paged_attention_decode_supports.restype = _I
     lib.cib_gemm_tcgen05_supports.argtypes = [_I, _I, _I]
@@ -380,6 +386,56 @@ def latent_attention_generic(q_abs: torch.Tensor, q: torch.Tensor, out: torch.Te
         T, num_heads, rk, dr, float(scale), int(window), _stream())
     _check(rc, "latent_attention_generic")
     _count()
+
+
+def latent_attention_mma_supports(rk: int, dr: int, dn: int) -> bool:
+    return bool(library().cib_latent_attention_mma_supports(rk, dr, dn))
+
+
+def latent_attention_splits(row_tiles: int, head_blocks: int, max_seq_len: int, ctas: int = 296) -> int:
+    """Over how many CTAs the keys of one query tile are split: enough to occupy the GPU when the tiles alone do not (a
+    decode step), each split keeping at least 128 keys."""
+    base = max(1, row_tiles * head_blocks)
+    if base >= ctas // 2:
+        return 1
+    return max(1, min(ctas // base, max_seq_len // 128, 64))
+
+
+def latent_attention_mma(q_abs: torch.Tensor, q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor,
+                         block_table: torch.Tensor, query_start_loc: torch.Tensor, seq_lens: torch.Tensor,
+                         query_lens: list, freq: torch.Tensor | None, rot_dims: int, sinks: torch.Tensor | None,
+                         num_heads: int, dn: int, rk: int, dr: int, scale: float, max_seq_len: int) -> None:
+    """The bfloat16 tensor-core form of :func:`latent_attention_generic` (same operands, ``q_abs`` in bfloat16; no
+    window).  ``query_lens``: tokens per request as host integers, an upper bound in a captured step (CTAs that find
+    no request leave); ``max_seq_len``: the longest context, which decides how a decode step's keys are split."""
+    T = q.shape[0]
+    R = seq_lens.numel()
+    if q_abs.shape != (T, num_heads * rk) or out.shape != (T, num_heads * rk) or q.shape[1] != num_heads * (dn + dr):
+        raise KernelError("latent_attention: q_abs / q / out do not fit the sizes")
+    for name, t in (("q_abs", q_abs), ("q", q), ("out", out), ("cache", cache)):
+        if t.dtype != torch.bfloat16 or t.stride(-1) != 1:
+            raise KernelError(f"latent_attention_mma: {name} must be bfloat16 with dense rows")
+    if cache.dim() != 5 or tuple(cache.shape[1:3]) != (1, 1) or cache.shape[4] != rk + dr:
+        raise KernelError(f"latent_attention: cache must be [pages, 1, 1, page_size, {rk + dr}], got {list(cache.shape)}")
+    if sinks is not None and (sinks.numel() != num_heads or sinks.dtype != torch.float32):
+        raise KernelError("latent_attention_mma: one 32-bit sink per head")
+    lib = library()
+    lens = (ctypes.c_int * len(query_lens))(*query_lens)
+    tiles = lib.cib_latent_attention_mma_tiles(lens, len(query_lens), num_heads)
+    head_blocks = -(-num_heads // 64) if num_heads > 64 else 1
+    splits = latent_attention_splits(tiles, head_blocks, max_seq_len)
+    scratch = torch.empty(T * num_heads * splits * (rk + 2), dtype=torch.float32, device=q.device) if splits > 1 else None
+    rc = lib.cib_latent_attention_mma(
+        _cuda(q_abs, "q_abs", contiguous=False), q_abs.stride(0), _cuda(q, "q", contiguous=False), q.stride(0), dn,
+        _cuda(out, "out", contiguous=False), out.stride(0), _cuda(scratch, "scratch") if scratch is not None else None,
+        _cuda(cache, "cache"), cache.shape[0], cache.shape[3], _cuda(block_table, "block_table", torch.int32),
+        block_table.stride(0), _cuda(query_start_loc, "query_start_loc", torch.int32), _cuda(seq_lens, "seq_lens", torch.int32),
+        R, tiles, _cuda(freq, "freq", torch.float32) if freq is not None else None, rot_dims if freq is not None else 0,
+        _cuda(sinks, "sinks") if sinks is not None else None, T, num_heads, rk, dr, float(scale), splits, _stream())
+    _check(rc, "latent_attention_mma")
+    _count()
+    if splits > 1:
+        _count()
 
 
 _decode_counters: dict = {}

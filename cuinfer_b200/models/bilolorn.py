@@ -28,7 +28,7 @@ from ..parts.spec import LayerSpec, ModelSpec, PartSpec
 
 ARCHITECTURE = "Bilolorn"
 # The design has no table of positions and hence no largest position of its own; this bounds what one request may hold.
-MAX_POSITIONS = 1 << 20
+MAX_POSITIONS = 1 << 17
 
 
 def _obj(raw: Mapping[str, Any], key: str, where: str, optional: bool = False) -> Optional[Mapping[str, Any]]:

@@ -29,6 +29,7 @@ from typing import Dict, List, Optional
 import torch
 
 from .. import kernels
+from . import attention_dispatch
 from .base import Mixer
 from .context import StepContext
 from .linear import Linear
@@ -37,6 +38,20 @@ from .spec import PagedCacheNeed, PartSpec, TensorSpec
 
 _DEFAULT_NAMES = {"dq": "dq", "dq_norm": "dq.norm", "uq": "uq", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk",
                   "uv": "uv", "sink": "sink", "g": "g", "o": "o"}
+
+
+def per_head_products(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[h] = a[h] @ w[h]^T`` for every head h; ``a [H, T, K]`` and ``out [H, T, N]`` are views of rows in which
+    the heads lie side by side, ``w [H, N, K]`` is dense.  bfloat16 with sizes in multiples of 8: the library's
+    strided batched product (as for the plain projections); else the FMA kernel, which is also the 32-bit path."""
+    H, T, K = a.shape
+    N = w.shape[1]
+    if (a.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and K % 8 == 0 and N % 8 == 0
+            and a.stride(1) % 8 == 0 and a.stride(0) % 8 == 0 and out.stride(1) % 8 == 0 and out.stride(0) % 8 == 0 and T > 0):
+        torch.bmm(a, w.transpose(1, 2), out=out)
+        kernels.launch_count += 1
+        return
+    kernels.gemm_generic_batched(a, w, out)
 
 
 @MIXERS.register("latent_attention")
@@ -145,15 +160,15 @@ class LatentAttention(Mixer):
                             freq, self.position.rotary_dim, kv.group.slot_mapping if kv.writes else None,
                             kv.cache if kv.writes else None, cq)
         q = self.uq.forward(cq)                                              # [T, H (dim + rot_dim)]
-        q_abs = torch.empty((T, H * rk), dtype=torch.float32, device=q.device)
-        kernels.gemm_generic_batched(q.view(T, H, dn + dr)[:, :, :dn].transpose(0, 1), self.uk_t,
-                                     q_abs.view(T, H, rk).transpose(0, 1))
+        # the tensor-core kernel takes the absorbed queries in bfloat16; the all-sizes kernel keeps them in 32 bits
+        fast = attention_dispatch.latent_tensor_cores(q.dtype, rk, dr, dn, self.window)
+        q_abs = torch.empty((T, H * rk), dtype=torch.bfloat16 if fast else torch.float32, device=q.device)
+        per_head_products(q.view(T, H, dn + dr)[:, :, :dn].transpose(0, 1), self.uk_t, q_abs.view(T, H, rk).transpose(0, 1))
         latent = torch.empty((T, H * rk), dtype=q.dtype, device=q.device)
-        kernels.latent_attention_generic(q_abs, q, latent, kv.cache, kv.group.block_table, ctx.query_start_loc, ctx.seq_lens,
-                                         ctx.token_request, ctx.positions, freq, self.position.rotary_dim, self.sinks,
-                                         H, dn, rk, dr, self.scale, self.window)
+        attention_dispatch.latent_attention(q_abs, q, latent, kv, ctx, freq, self.position.rotary_dim, self.sinks,
+                                            H, dn, rk, dr, self.scale, self.window)
         heads = torch.empty((T, self.v_size), dtype=q.dtype, device=q.device)
-        kernels.gemm_generic_batched(latent.view(T, H, rk).transpose(0, 1), self.uv, heads.view(T, H, self.vdim).transpose(0, 1))
+        per_head_products(latent.view(T, H, rk).transpose(0, 1), self.uv, heads.view(T, H, self.vdim).transpose(0, 1))
         if self.has_gate:
             gated = torch.empty_like(heads)
             kernels.sigmoid_gate(heads, down[:, self.q_rank + self.row:], gated)

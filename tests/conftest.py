@@ -75,15 +75,17 @@ GAINS = {"float32": {"q_norm": 3.0, "k_norm": 1.5}, "bfloat16": {"q_norm": 2.0, 
 WORST_ERRORS = {}
 
 
-def note_error(dtype: str, where: str, err: float) -> None:
-    if err > WORST_ERRORS.get(dtype, ("", -1.0))[1]:
-        WORST_ERRORS[dtype] = (where, err)
+def note_error(dtype: str, where: str, err: float, family: str = "") -> None:
+    """``family``: tests of another model family, whose error measure and bound are their own, are listed apart."""
+    key = f"{dtype} {family}".strip()
+    if err > WORST_ERRORS.get(key, ("", -1.0))[1]:
+        WORST_ERRORS[key] = (where, err)
 
 
 def pytest_terminal_summary(terminalreporter):
     for dtype, (where, err) in sorted(WORST_ERRORS.items()):
-        terminalreporter.write_line(f"largest {dtype} error against the plain implementation: {err:.3e} of the largest "
-                                    f"logit ({where}); allowed {TOLERANCE[dtype]:.1e}")
+        allowed = f"; allowed {TOLERANCE[dtype]:.1e}" if dtype in TOLERANCE else ""
+        terminalreporter.write_line(f"largest {dtype} error against the plain implementation: {err:.3e} ({where}){allowed}")
 
 
 @pytest.fixture(scope="session")

@@ -26,11 +26,12 @@ def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
 
 
 def rotate_interleaved(x: torch.Tensor, positions: torch.Tensor, base: float, dims: int) -> torch.Tensor:
-    """x [..., T, d]: element 2i pairs with 2i+1 for i < dims/2; the rest of d passes unchanged."""
+    """x [..., T, d]: element 2i pairs with 2i+1 for i < dims/2; the rest of d passes unchanged.  Frequencies and
+    angles are 32-bit numbers, as the design has them; sine and cosine are taken in x's type."""
     out = x.clone()
     for i in range(dims // 2):
-        f = base ** (-2.0 * i / dims)
-        a = positions.to(x.dtype) * f
+        f = torch.tensor(base ** (-2.0 * i / dims), dtype=torch.float32)
+        a = (positions.to(torch.float32) * f).to(x.dtype)
         c, s = torch.cos(a), torch.sin(a)
         u, v = x[..., 2 * i], x[..., 2 * i + 1]
         out[..., 2 * i] = u * c - v * s

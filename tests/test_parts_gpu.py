@@ -248,7 +248,7 @@ def test_toy_mixer_with_state_registers_builds_and_steps(dtype, tmp_path):
     requests = {f"r{i}": random_tokens(V, n, 500 + i) for i, n in enumerate([40, 23, 66, 31, 52])}
     _replay_all(folder, dtype, requests, tmp_path, lambda ids: _toy_plain(pcfg, w, ids))
     runner = replay.make_runner(folder, dtype, 128, 16)
-    assert sorted(runner.storage.state) == [0, 2] and runner.storage.state[0].shape == (8, H + 1)
+    assert sorted(runner.storage.state) == [0, 2] and runner.storage.state[0].shape == (4, H + 1)
     assert [g.runs for g in runner.groups] == [(1,)]
 
 
