@@ -2,9 +2,10 @@
 // 32-bit accumulation), for prompt portions, mixed batches and decode steps alike.  What it computes is stated at
 // the head of attention_latent.cu; this file is the bfloat16 path for rk and dr that are multiples of 16, rk <= 512.
 //
-// All heads read the same rows, so a CTA's 64-row query tile is (tokens x heads) of ONE request: HB = 2^k heads side
-// by side (k smallest with HB >= min(H, 64)) times 64 / HB consecutive tokens; a decode step's single token fills the
-// tile with its heads.  Keys come in tiles of 32 rows through two cp.async stages; S = Q K^T runs over all rk + dr
+// All heads read the same rows, so a CTA's query tile of M = 64 rows is (tokens x heads) of ONE request: HB = 2^k heads
+// side by side (k smallest with HB >= min(H, M)) times M / HB consecutive tokens; a decode step's single token fills the
+// tile with its heads, and with 32 heads or fewer a decode step runs tiles of M = 32 rows (no idle rows, and two CTAs
+// to an SM).  Keys come in tiles of 32 rows through two cp.async stages; S = Q K^T runs over all rk + dr
 // columns, O += P V over the first rk columns of the same shared-memory tile (the values ARE the latents).  A warp owns
 // 16 rows; for rk > 256 eight warps share them in pairs, each computing S again and keeping half of the value columns
 // (128 accumulator registers a thread).  The query's rotary part is encoded as the tile is loaded; softmax statistics
@@ -17,12 +18,11 @@
 
 namespace cib {
 
-constexpr int kLmM = 64;       // query rows of a tile
-constexpr int kLmN = 32;       // keys of a tile
+constexpr int kLmN = 32;       // keys of a tile (a query tile has 16 * RG rows)
 constexpr float kLog2e = 1.4426950408889634f;
 
-template <int RKH, int CS>
-__global__ void __launch_bounds__(128 * CS)
+template <int RKH, int CS, int RG>
+__global__ void __launch_bounds__(32 * RG * CS)
 latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_abs, int qa_stride, const __nv_bfloat16* __restrict__ q,
                             int q_stride, int dn, __nv_bfloat16* __restrict__ out, int out_stride, float* __restrict__ part,
                             const __nv_bfloat16* __restrict__ cache, int num_pages, int page_size,
@@ -32,7 +32,8 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_abs, int qa_stri
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ int s_req, s_tile;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int rg = warp & 3, ch = warp >> 2;               // row group of 16 rows; which half of the value columns
+    constexpr int kLmM = 16 * RG;
+    const int rg = warp % RG, ch = warp / RG;              // row group of 16 rows; which half of the value columns
     const int qrow = lane >> 2, quad = lane & 3;
     const int D = rk + dr, LD = D + 8;                     // rows 16 bytes longer than D: ldmatrix hits every bank once
     const int HB = 1 << hb_log2, TM = kLmM >> hb_log2;
@@ -67,21 +68,22 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_abs, int qa_stri
     const int per = (tiles_all + splits - 1) / splits;
     const int t_begin = split * per, t_end = min(tiles_all, t_begin + per);
 
-    auto load_keys = [&](int s, int key0) {
-        __nv_bfloat16* dst = stage(s);
-        const int chunks = D / 8;
-        for (int idx = tid; idx < kLmN * chunks; idx += blockDim.x) {
-            const int row = idx / chunks, chunk = idx % chunks;
-            const int key = key0 + row;
-            bool ok = key < k_hi;
-            int page = 0;
-            if (ok) {
-                page = table[key / page_size];
-                ok = page >= 0 && page < num_pages;
-            }
-            const __nv_bfloat16* src = cache + ((size_t)(ok ? page : 0) * page_size + (ok ? key % page_size : 0)) * D + chunk * 8;
-            cp_async16(dst + row * LD + chunk * 8, src, ok);
-        }
+    // A key row of a tile is copied by blockDim.x / 32 threads, 16 bytes at a time.  Its page number is looked up one
+    // tile ahead (`page_of`), so that no copy waits for a block-table entry: with the lookup inside the copy loop every
+    // 16-byte chunk stalled its thread for a trip to the L2, 8 us a tile.
+    const int tpr = blockDim.x / kLmN;
+    const int lrow = tid / tpr, lsub = tid % tpr;
+    auto page_of = [&](int key0) {
+        const int key = key0 + lrow;
+        if (key >= k_hi) return -1;
+        const int page = table[key / page_size];
+        return (page >= 0 && page < num_pages) ? page : -1;
+    };
+    auto load_keys = [&](int s, int key0, int page) {
+        const bool ok = page >= 0;
+        const __nv_bfloat16* src = cache + ((size_t)(ok ? page : 0) * page_size + (ok ? (key0 + lrow) % page_size : 0)) * D;
+        __nv_bfloat16* dst = stage(s) + lrow * LD;
+        for (int chunk = lsub; chunk < D / 8; chunk += tpr) cp_async16(dst + chunk * 8, src + chunk * 8, ok);
     };
 
     // ---- query tile: [Uk^T q_plain (rk) | rot(q_rot) (dr)] per (token, head) row ----
@@ -114,8 +116,9 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_abs, int qa_stri
             *reinterpret_cast<uint32_t*>(sQ + row * LD + rk + 2 * i) = pack_bf16(u, v);
         }
     }
-    if (t_begin < t_end) load_keys(0, t_begin * kLmN);
+    if (t_begin < t_end) load_keys(0, t_begin * kLmN, page_of(t_begin * kLmN));
     cp_async_commit();
+    int page_next = t_begin + 1 < t_end ? page_of((t_begin + 1) * kLmN) : -1;
 
     int pos_row[2], head_row[2];
     bool row_ok[2];
@@ -144,7 +147,10 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_abs, int qa_stri
 
     for (int t = t_begin; t < t_end; ++t) {
         const int key0 = t * kLmN;
-        if (t + 1 < t_end) load_keys((t + 1 - t_begin) & 1, key0 + kLmN);
+        if (t + 1 < t_end) {
+            load_keys((t + 1 - t_begin) & 1, key0 + kLmN, page_next);
+            page_next = t + 2 < t_end ? page_of(key0 + 2 * kLmN) : -1;
+        }
         cp_async_commit();
         cp_async_wait<1>();
         __syncthreads();
@@ -269,11 +275,11 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_abs, int qa_stri
 }
 
 // Merge the splits of a (token, head): M = max(sink, m_s), L = 2^(sink - M) + sum l_s 2^(m_s - M),
-// out = sum acc_s 2^(m_s - M) / L.  A warp per (token, head).
+// out = sum acc_s 2^(m_s - M) / L.  A block per (token, head), a thread per column.
 __global__ void latent_attention_merge_kernel(const float* __restrict__ part, const float* __restrict__ sinks,
                                               __nv_bfloat16* __restrict__ out, int out_stride, int H, int rk, int splits,
                                               int rows) {
-    const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    const int w = blockIdx.x, lane = threadIdx.x;
     if (w >= rows) return;
     const int token = w / H, head = w % H;
     const float* p = part + (size_t)w * splits * (rk + 2);
@@ -286,8 +292,9 @@ __global__ void latent_attention_merge_kernel(const float* __restrict__ part, co
         if (m != -INFINITY) L += p[(size_t)s * (rk + 2) + 1] * exp2f(m - M);
     }
     const float inv = L > 0.f ? 1.f / L : 0.f;
-    for (int c = lane; c < rk; c += 32) {
+    for (int c = lane; c < rk; c += blockDim.x) {
         float acc = 0.f;
+#pragma unroll 4
         for (int s = 0; s < splits; ++s) {
             const float m = p[(size_t)s * (rk + 2)];
             if (m != -INFINITY) acc += p[(size_t)s * (rk + 2) + 2 + c] * exp2f(m - M);
@@ -296,15 +303,15 @@ __global__ void latent_attention_merge_kernel(const float* __restrict__ part, co
     }
 }
 
-template <int RKH, int CS>
+template <int RKH, int CS, int RG>
 static int launch_latent_mma(dim3 grid, size_t smem, cudaStream_t stream, const void* q_abs, int qa_stride, const void* q,
                              int q_stride, int dn, void* out, int out_stride, float* part, const void* cache, int num_pages,
                              int page_size, const int* bt, int ts, const int* qsl, const int* sl, int R, const float* freq,
                              int rot_dims, const float* sinks, int H, int hb_log2, int rk, int dr, float scale_log2) {
     static SmemLimit limit;
-    auto kernel = latent_attention_mma_kernel<RKH, CS>;
+    auto kernel = latent_attention_mma_kernel<RKH, CS, RG>;
     if (smem > 48 * 1024 && raise_smem_limit(limit, kernel, 200 * 1024, "latent_attention_mma") != 0) return -2;
-    kernel<<<grid, 128 * CS, smem, stream>>>((const __nv_bfloat16*)q_abs, qa_stride, (const __nv_bfloat16*)q, q_stride, dn,
+    kernel<<<grid, 32 * RG * CS, smem, stream>>>((const __nv_bfloat16*)q_abs, qa_stride, (const __nv_bfloat16*)q, q_stride, dn,
                                              (__nv_bfloat16*)out, out_stride, part, (const __nv_bfloat16*)cache, num_pages,
                                              page_size, bt, ts, qsl, sl, R, freq, rot_dims, sinks, H, hb_log2, rk, dr,
                                              scale_log2);
@@ -319,16 +326,16 @@ extern "C" int cib_latent_attention_mma_supports(int rk, int dr, int dn) {
     return rk > 0 && rk % 16 == 0 && rk <= 512 && dr >= 0 && dr % 16 == 0 && dn >= 0;
 }
 
-// Heads side by side in a query tile: the smallest power of two that holds min(H, 64) heads.
-static int head_block_log2(int H) {
+// Heads side by side in a query tile of `rows` rows: the smallest power of two that holds min(H, rows) heads.
+static int head_block_log2(int H, int rows) {
     int k = 0;
-    while ((1 << k) < H && k < 6) ++k;
+    while ((1 << k) < H && (1 << k) < rows) ++k;
     return k;
 }
 
-// Row tiles a launch needs for requests of these numbers of new tokens.
-extern "C" int cib_latent_attention_mma_tiles(const int* query_lens, int num_requests, int H) {
-    const int tm = kLmM >> head_block_log2(H);
+// Row tiles a launch needs for requests of these numbers of new tokens, with query tiles of `rows` (64 or 32) rows.
+extern "C" int cib_latent_attention_mma_tiles(const int* query_lens, int num_requests, int H, int rows) {
+    const int tm = rows >> head_block_log2(H, rows);
     long long tiles = 0;
     for (int i = 0; i < num_requests; ++i) tiles += (query_lens[i] + tm - 1) / tm;
     return (int)(tiles > 0x7fffffff ? 0x7fffffff : tiles);
@@ -338,7 +345,7 @@ extern "C" int cib_latent_attention_mma_tiles(const int* query_lens, int num_req
 extern "C" int cib_latent_attention_mma(const void* q_abs, int qa_stride, const void* q, int q_stride, int dn, void* out,
                                         int out_stride, float* scratch, const void* cache, int num_pages, int page_size,
                                         const int* block_table, int table_stride, const int* query_start_loc,
-                                        const int* seq_lens, int num_requests, int row_tiles, const float* freq,
+                                        const int* seq_lens, int num_requests, int row_tiles, int tile_rows, const float* freq,
                                         int rot_dims, const float* sinks, int num_tokens, int H, int rk, int dr, float scale,
                                         int splits, cudaStream_t stream) {
     CIB_REQUIRE(cib_latent_attention_mma_supports(rk, dr, dn), "latent_attention_mma: sizes rk=%d dr=%d are not taken", rk, dr);
@@ -347,28 +354,31 @@ extern "C" int cib_latent_attention_mma(const void* q_abs, int qa_stride, const 
     CIB_REQUIRE(rot_dims >= 0 && rot_dims <= dr && rot_dims % 2 == 0 && (rot_dims == 0 || freq), "latent_attention_mma: bad rotary part");
     CIB_REQUIRE(qa_stride % 8 == 0 && out_stride % 2 == 0, "latent_attention_mma: rows must start on 16-byte boundaries");
     CIB_REQUIRE(splits >= 1 && splits <= 65535 && (splits == 1 || scratch != nullptr), "latent_attention_mma: bad split");
+    CIB_REQUIRE(tile_rows == 64 || tile_rows == 32, "latent_attention_mma: query tiles have 64 or 32 rows");
     if (num_tokens == 0 || row_tiles == 0) return 0;
-    const int hb_log2 = head_block_log2(H);
+    const int hb_log2 = head_block_log2(H, tile_rows);
     dim3 grid(row_tiles, (H + (1 << hb_log2) - 1) >> hb_log2, splits);
     const int D = rk + dr;
-    const size_t smem = (size_t)(kLmM + 2 * kLmN) * (D + 8) * sizeof(__nv_bfloat16);
+    const size_t smem = (size_t)(tile_rows + 2 * kLmN) * (D + 8) * sizeof(__nv_bfloat16);
     const float scale_log2 = scale * kLog2e;
     int rc;
-#define CIB_LM_GO(RKH, CS)                                                                                                 \
-    rc = launch_latent_mma<RKH, CS>(grid, smem, stream, q_abs, qa_stride, q, q_stride, dn, out, out_stride, scratch, cache,  \
-                                    num_pages, page_size, block_table, table_stride, query_start_loc, seq_lens, num_requests, \
-                                    freq, rot_dims, sinks, H, hb_log2, rk, dr, scale_log2)
+#define CIB_LM_ARGS                                                                                                        \
+    grid, smem, stream, q_abs, qa_stride, q, q_stride, dn, out, out_stride, scratch, cache, num_pages, page_size, block_table, \
+        table_stride, query_start_loc, seq_lens, num_requests, freq, rot_dims, sinks, H, hb_log2, rk, dr, scale_log2
+#define CIB_LM_GO(RKH, CS) \
+    rc = tile_rows == 64 ? launch_latent_mma<RKH, CS, 4>(CIB_LM_ARGS) : launch_latent_mma<RKH, CS, 2>(CIB_LM_ARGS)
     if (rk <= 32) CIB_LM_GO(32, 1);
     else if (rk <= 64) CIB_LM_GO(64, 1);
     else if (rk <= 128) CIB_LM_GO(128, 1);
     else if (rk <= 256) CIB_LM_GO(256, 1);
     else CIB_LM_GO(256, 2);
 #undef CIB_LM_GO
+#undef CIB_LM_ARGS
     if (rc != 0) return rc;
     CIB_LAUNCH_CHECK("latent_attention_mma");
     if (splits > 1) {
         const int rows = num_tokens * H;
-        latent_attention_merge_kernel<<<(rows + 3) / 4, 128, 0, stream>>>(scratch, sinks, (__nv_bfloat16*)out, out_stride, H, rk,
+        latent_attention_merge_kernel<<<rows, rk >= 256 ? 256 : 128, 0, stream>>>(scratch, sinks, (__nv_bfloat16*)out, out_stride, H, rk,
                                                                            splits, rows);
         CIB_LAUNCH_CHECK("latent_attention_merge");
     }

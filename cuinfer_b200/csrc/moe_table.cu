@@ -116,3 +116,252 @@ extern "C" int cib_moe_table_down(const void* act, int dtype, const int* ids, co
     CIB_LAUNCH_CHECK("moe_table_down");
     return 0;
 }
+
+// ---- many tokens: rows sorted by expert, then one tensor-core product per expert group ---------------------------------
+// A prompt portion gives every expert many rows, so the experts' matrices are worth reading once per 64-row tile
+// instead of once per token.  Everything is decided on the device (the step may be replayed from a CUDA graph):
+//   route   : count the (token, choice) slots of every expert, lay the slots out expert by expert, and list the
+//             64-row tiles of every group (one block; the order of slots inside a group is whatever the atomics give,
+//             which changes no result: every row is computed on its own)
+//   grouped : out rows of a tile = A rows x W_e^T on mma.sync m16n8k16 — with A gathered through the slot list and
+//             silu(gate) * up as the epilogue for the first product, plain for the second
+//   combine : out[t] = base[t] + weight * sum over the token's slots of its down-projected rows
+#include "mma_utils.cuh"
+
+namespace cib {
+
+constexpr int kGM = 64, kGN = 64, kGK = 32, kGStages = 3, kGLd = kGK + 8;
+
+__global__ void __launch_bounds__(1024)
+moe_route_kernel(const int* __restrict__ ids, const int* __restrict__ table, int vocab, int top, int experts, int slots,
+                 int* __restrict__ sorted_slot, int* __restrict__ slot_pos, int* __restrict__ offsets,
+                 int* __restrict__ tile_expert, int* __restrict__ tile_row0, int* __restrict__ num_tiles, int max_tiles) {
+    extern __shared__ int route_s[];                    // counts[E], cursor[E], start[E + 1]
+    int* counts = route_s;
+    int* cursor = route_s + experts;
+    int* start = route_s + 2 * experts;
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) { counts[e] = 0; cursor[e] = 0; }
+    __syncthreads();
+    auto expert_of = [&](int slot) {
+        const int id = ids[slot / top];
+        const int e = (id >= 0 && id < vocab) ? table[(size_t)id * top + slot % top] : -1;
+        return (e >= 0 && e < experts) ? e : -1;
+    };
+    for (int s = threadIdx.x; s < slots; s += blockDim.x) {
+        const int e = expert_of(s);
+        if (e >= 0) atomicAdd(&counts[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0, tiles = 0;
+        for (int e = 0; e < experts; ++e) {
+            start[e] = at;
+            for (int r = 0; r < counts[e] && tiles < max_tiles; r += kGM) {
+                tile_expert[tiles] = e;
+                tile_row0[tiles] = at + r;
+                ++tiles;
+            }
+            at += counts[e];
+        }
+        start[experts] = at;
+        *num_tiles = tiles;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e <= experts; e += blockDim.x) offsets[e] = start[e];
+    for (int s = threadIdx.x; s < slots; s += blockDim.x) {
+        const int e = expert_of(s);
+        int at = -1;
+        if (e >= 0) {
+            at = start[e] + atomicAdd(&cursor[e], 1);
+            sorted_slot[at] = s;
+        }
+        slot_pos[s] = at;
+    }
+}
+
+// out[r, n] for the rows r of one tile of one expert's group; w: [E][N_total][K] with the expert's rows `w_expert`
+// elements apart.  GATED: columns j and N + j of the expert are gate and up, out[r, j] = silu(gate) * up, out has N
+// columns.  Otherwise out[r, j] for 128 columns a CTA.  `gather`: row r of A is a[(gather[r] / top)]; else a[r].
+template <bool GATED>
+__global__ void __launch_bounds__(128)
+moe_grouped_gemm_kernel(const __nv_bfloat16* __restrict__ a, int lda, const int* __restrict__ gather, int top,
+                        const __nv_bfloat16* __restrict__ w, long long w_expert, __nv_bfloat16* __restrict__ out, int ldo,
+                        const int* __restrict__ offsets, const int* __restrict__ tile_expert,
+                        const int* __restrict__ tile_row0, const int* __restrict__ num_tiles, int N, int K) {
+    __shared__ __align__(16) __nv_bfloat16 sA[kGStages][kGM][kGLd];
+    __shared__ __align__(16) __nv_bfloat16 sB[kGStages][2][kGN][kGLd];
+    if ((int)blockIdx.x >= *num_tiles) return;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int e = tile_expert[blockIdx.x];
+    const int r0 = tile_row0[blockIdx.x];
+    const int rows = min(kGM, offsets[e + 1] - r0);
+    const int n0 = blockIdx.y * (GATED ? kGN : 2 * kGN);
+    const int second = GATED ? N : kGN;                       // where the second 64-column tile's weight rows start
+    const __nv_bfloat16* we = w + (size_t)e * w_expert;
+
+    // what this thread copies per stage: two 16-byte chunks of A, four of B
+    const __nv_bfloat16* a_src[2];
+    bool a_ok[2];
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+        const int idx = tid + c * 128, row = idx >> 2;
+        a_ok[c] = row < rows;
+        const int src_row = a_ok[c] ? (gather ? gather[r0 + row] / top : r0 + row) : 0;
+        a_src[c] = a + (size_t)src_row * lda + (idx & 3) * 8;
+    }
+    const __nv_bfloat16* b_src[4];
+    bool b_ok[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        const int idx = tid + c * 128, half = idx >> 8, row = (idx >> 2) & 63;
+        const int col = n0 + row;                              // output column of this weight row within its half
+        b_ok[c] = GATED ? col < N : col + half * kGN < N;
+        b_src[c] = we + (size_t)(b_ok[c] ? half * second + col : 0) * K + (idx & 3) * 8;
+    }
+    auto load = [&](int stage, int k0) {
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            const int idx = tid + c * 128;
+            cp_async16(&sA[stage][idx >> 2][(idx & 3) * 8], a_src[c] + k0, a_ok[c]);
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int idx = tid + c * 128;
+            cp_async16(&sB[stage][idx >> 8][(idx >> 2) & 63][(idx & 3) * 8], b_src[c] + k0, b_ok[c]);
+        }
+    };
+
+    float acc[2][kGN / 8][4];
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int i = 0; i < kGN / 8; ++i) { acc[h][i][0] = acc[h][i][1] = acc[h][i][2] = acc[h][i][3] = 0.f; }
+
+    const int steps = K / kGK;
+#pragma unroll
+    for (int s = 0; s < kGStages - 1; ++s) {
+        if (s < steps) load(s, s * kGK);
+        cp_async_commit();
+    }
+    const int mat = lane >> 3, rr = lane & 7;
+    for (int ks = 0; ks < steps; ++ks) {
+        cp_async_wait<kGStages - 2>();
+        __syncthreads();
+        if (ks + kGStages - 1 < steps) load((ks + kGStages - 1) % kGStages, (ks + kGStages - 1) * kGK);
+        cp_async_commit();
+        const int st = ks % kGStages;
+#pragma unroll
+        for (int kk = 0; kk < kGK / 16; ++kk) {
+            uint32_t af[4];
+            ldmatrix_x4(af, smem_u32(&sA[st][warp * 16 + (mat & 1) * 8 + rr][kk * 16 + (mat >> 1) * 8]));
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                for (int np = 0; np < kGN / 16; ++np) {
+                    uint32_t b[4];
+                    ldmatrix_x4(b, smem_u32(&sB[st][h][np * 16 + (mat >> 1) * 8 + rr][kk * 16 + (mat & 1) * 8]));
+                    mma_bf16_16816(acc[h][2 * np], af, b[0], b[1]);
+                    mma_bf16_16816(acc[h][2 * np + 1], af, b[2], b[3]);
+                }
+            }
+        }
+    }
+    cp_async_wait<0>();
+
+    const int qrow = lane >> 2, quad = lane & 3;
+#pragma unroll
+    for (int hrow = 0; hrow < 2; ++hrow) {
+        const int row = warp * 16 + qrow + 8 * hrow;
+        if (row >= rows) continue;
+        __nv_bfloat16* dst = out + (size_t)(r0 + row) * ldo;
+        if (GATED) {
+#pragma unroll
+            for (int nt = 0; nt < kGN / 8; ++nt) {
+                const int col = n0 + nt * 8 + quad * 2;
+                const float g0 = acc[0][nt][2 * hrow], g1 = acc[0][nt][2 * hrow + 1];
+                const float v0 = g0 / (1.f + expf(-g0)) * acc[1][nt][2 * hrow];
+                const float v1 = g1 / (1.f + expf(-g1)) * acc[1][nt][2 * hrow + 1];
+                if (col + 1 < N) *reinterpret_cast<uint32_t*>(dst + col) = pack_bf16(v0, v1);
+                else if (col < N) dst[col] = __float2bfloat16_rn(v0);
+            }
+        } else {
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int nt = 0; nt < kGN / 8; ++nt) {
+                    const int col = n0 + h * kGN + nt * 8 + quad * 2;
+                    if (col + 1 < N) *reinterpret_cast<uint32_t*>(dst + col) = pack_bf16(acc[h][nt][2 * hrow], acc[h][nt][2 * hrow + 1]);
+                    else if (col < N) dst[col] = __float2bfloat16_rn(acc[h][nt][2 * hrow]);
+                }
+        }
+    }
+}
+
+__global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ slot_pos, int top,
+                                   const __nv_bfloat16* __restrict__ base, int base_stride, float weight,
+                                   __nv_bfloat16* __restrict__ out, int width) {
+    const int t = blockIdx.x;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float sum = 0.f;
+        for (int k = 0; k < top; ++k) {
+            const int at = slot_pos[t * top + k];
+            if (at >= 0) sum += __bfloat162float(y[(size_t)at * width + i]);
+        }
+        float v = sum * weight;
+        if (base) v += __bfloat162float(base[(size_t)t * base_stride + i]);
+        out[(size_t)t * width + i] = __float2bfloat16_rn(v);
+    }
+}
+
+}  // namespace cib
+
+extern "C" int cib_moe_table_grouped_supports(int width, int ff, int experts) {
+    return width % cib::kGK == 0 && ff % cib::kGK == 0 && experts > 0 && experts <= 4096;
+}
+
+// Integers of workspace the grouped path needs: sorted slots, their inverse, group offsets, the tile list, the tile count.
+extern "C" long long cib_moe_table_grouped_workspace_ints(int num_tokens, int top, int experts) {
+    const long long slots = (long long)num_tokens * top;
+    const long long max_tiles = (slots + cib::kGM - 1) / cib::kGM + experts;
+    return 2 * slots + (experts + 1) + 2 * max_tiles + 1;
+}
+
+// bfloat16 only.  act: [T * top, ff] and y: [T * top, width] scratch rows; ints: see above.
+extern "C" int cib_moe_table_grouped(const void* h, int h_stride, const int* ids, const int* table, int vocab, int top,
+                                     int experts, const void* gate_up, const void* down, const void* base, int base_stride,
+                                     float weight, void* out, void* act, void* y, int* ints, int num_tokens, int width,
+                                     int ff, cudaStream_t stream) {
+    using namespace cib;
+    CIB_REQUIRE(num_tokens >= 0 && top > 0 && vocab > 0, "moe_table_grouped: bad sizes");
+    CIB_REQUIRE(cib_moe_table_grouped_supports(width, ff, experts), "moe_table_grouped: width %d / ff %d / %d experts are not taken", width, ff, experts);
+    CIB_REQUIRE(h_stride % 8 == 0, "moe_table_grouped: rows must start on 16-byte boundaries");
+    if (num_tokens == 0) return 0;
+    const long long slots64 = (long long)num_tokens * top;
+    CIB_REQUIRE(slots64 < (1ll << 30), "moe_table_grouped: too many rows");
+    const int slots = (int)slots64;
+    const int max_tiles = (slots + kGM - 1) / kGM + experts;
+    int* sorted_slot = ints;
+    int* slot_pos = sorted_slot + slots;
+    int* offsets = slot_pos + slots;
+    int* tile_expert = offsets + experts + 1;
+    int* tile_row0 = tile_expert + max_tiles;
+    int* num_tiles = tile_row0 + max_tiles;
+    moe_route_kernel<<<1, 1024, (size_t)(3 * experts + 1) * sizeof(int), stream>>>(ids, table, vocab, top, experts, slots, sorted_slot,
+                                                                                   slot_pos, offsets, tile_expert, tile_row0,
+                                                                                   num_tiles, max_tiles);
+    CIB_LAUNCH_CHECK("moe_route");
+    dim3 g1(max_tiles, (ff + kGN - 1) / kGN);
+    moe_grouped_gemm_kernel<true><<<g1, 128, 0, stream>>>((const __nv_bfloat16*)h, h_stride, sorted_slot, top,
+                                                          (const __nv_bfloat16*)gate_up, (long long)2 * ff * width,
+                                                          (__nv_bfloat16*)act, ff, offsets, tile_expert, tile_row0, num_tiles, ff, width);
+    CIB_LAUNCH_CHECK("moe_grouped_gate_up");
+    dim3 g2(max_tiles, (width + 2 * kGN - 1) / (2 * kGN));
+    moe_grouped_gemm_kernel<false><<<g2, 128, 0, stream>>>((const __nv_bfloat16*)act, ff, nullptr, top, (const __nv_bfloat16*)down,
+                                                           (long long)width * ff, (__nv_bfloat16*)y, width, offsets, tile_expert,
+                                                           tile_row0, num_tiles, width, ff);
+    CIB_LAUNCH_CHECK("moe_grouped_down");
+    moe_combine_kernel<<<num_tokens, 256, 0, stream>>>((const __nv_bfloat16*)y, slot_pos, top, (const __nv_bfloat16*)base, base_stride,
+                                                       weight, (__nv_bfloat16*)out, width);
+    CIB_LAUNCH_CHECK("moe_combine");
+    return 0;
+}

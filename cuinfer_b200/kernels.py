@@ -74,11 +74,12 @@ def _declare(lib: ctypes.CDLL) -> None:
         "cib_latent_prep": [_P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _I, _F, _P, _P, _I, _P, _P, ctypes.c_longlong, _P, _I, _I, _P],
         "cib_latent_attention_generic": [_P, _I, _I, _P, _I, _I, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _P, _P, _P, _I, _P, _I,
                                          _I, _I, _I, _I, _F, _I, _P],
-        "cib_latent_attention_mma": [_P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _P, _I, _P, _P, _I, _I, _P, _I, _P, _I, _I, _I, _I,
+        "cib_latent_attention_mma": [_P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _P, _I, _P, _I, _I, _I, _I,
                                      _F, _I, _P],
         "cib_gemm_generic_batched": [_P, _I, ctypes.c_longlong, _P, _I, ctypes.c_longlong, _I, _P, _I, ctypes.c_longlong, _I,
                                      _I, _I, _I, _I, _P],
         "cib_moe_table_gate_up": [_P, _I, _I, _P, _P, _I, _I, _I, _P, _P, _I, _I, _I, _P],
+        "cib_moe_table_grouped": [_P, _I, _P, _P, _I, _I, _I, _P, _P, _P, _I, _F, _P, _P, _P, _P, _I, _I, _I, _P],
         "cib_moe_table_down": [_P, _I, _P, _P, _I, _I, _I, _P, _P, _I, _F, _P, _I, _I, _I, _P],
         "cib_add_rmsnorm": [_P, _P, _I, _P, _I, _F, _P, _I, _I, _I, _P],
         "cib_gather_rows": [_P, _P, _I, _P, _P, _I, _I, _I, _P],
@@ -101,9 +102,13 @@ def _declare(lib: ctypes.CDLL) -> None:
         fn = getattr(lib, name)
         fn.argtypes = argtypes
         fn.restype = _I
+    lib.cib_moe_table_grouped_supports.argtypes = [_I, _I, _I]
+    lib.cib_moe_table_grouped_supports.restype = _I
+    lib.cib_moe_table_grouped_workspace_ints.argtypes = [_I, _I, _I]
+    lib.cib_moe_table_grouped_workspace_ints.restype = ctypes.c_longlong
     lib.cib_latent_attention_mma_supports.argtypes = [_I, _I, _I]
     lib.cib_latent_attention_mma_supports.restype = _I
-    lib.cib_latent_attention_mma_tiles.argtypes = [_P, _I, _I]
+    lib.cib_latent_attention_mma_tiles.argtypes = [_P, _I, _I, _I]
     lib.cib_latent_attention_mma_tiles.restype = _I
     lib.cib_paged_attention_decode_supports.argtypes = [_I, _I, _I]
     lib.cib_paged_attention_decode_supports.restype = _I
@@ -394,20 +399,22 @@ def latent_attention_mma_supports(rk: int, dr: int, dn: int) -> bool:
 
 def latent_attention_splits(row_tiles: int, head_blocks: int, max_seq_len: int, ctas: int = 296) -> int:
     """Over how many CTAs the keys of one query tile are split: enough to occupy the GPU when the tiles alone do not (a
-    decode step), each split keeping at least 128 keys."""
+    decode step), each split keeping at least 64 keys."""
     base = max(1, row_tiles * head_blocks)
     if base >= ctas // 2:
         return 1
-    return max(1, min(ctas // base, max_seq_len // 128, 64))
+    return max(1, min(ctas // base, max_seq_len // 64, 64))
 
 
 def latent_attention_mma(q_abs: torch.Tensor, q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor,
                          block_table: torch.Tensor, query_start_loc: torch.Tensor, seq_lens: torch.Tensor,
                          query_lens: list, freq: torch.Tensor | None, rot_dims: int, sinks: torch.Tensor | None,
-                         num_heads: int, dn: int, rk: int, dr: int, scale: float, max_seq_len: int) -> None:
+                         num_heads: int, dn: int, rk: int, dr: int, scale: float, max_seq_len: int,
+                         decode_only: bool = False) -> None:
     """The bfloat16 tensor-core form of :func:`latent_attention_generic` (same operands, ``q_abs`` in bfloat16; no
     window).  ``query_lens``: tokens per request as host integers, an upper bound in a captured step (CTAs that find
-    no request leave); ``max_seq_len``: the longest context, which decides how a decode step's keys are split."""
+    no request leave); ``max_seq_len``: the longest context, which decides how a decode step's keys are split;
+    ``decode_only``: every request brings one token (query tiles of 32 rows then, when the heads fit)."""
     T = q.shape[0]
     R = seq_lens.numel()
     if q_abs.shape != (T, num_heads * rk) or out.shape != (T, num_heads * rk) or q.shape[1] != num_heads * (dn + dr):
@@ -421,7 +428,8 @@ def latent_attention_mma(q_abs: torch.Tensor, q: torch.Tensor, out: torch.Tensor
         raise KernelError("latent_attention_mma: one 32-bit sink per head")
     lib = library()
     lens = (ctypes.c_int * len(query_lens))(*query_lens)
-    tiles = lib.cib_latent_attention_mma_tiles(lens, len(query_lens), num_heads)
+    tile_rows = 32 if decode_only and num_heads <= 32 else 64
+    tiles = lib.cib_latent_attention_mma_tiles(lens, len(query_lens), num_heads, tile_rows)
     head_blocks = -(-num_heads // 64) if num_heads > 64 else 1
     splits = latent_attention_splits(tiles, head_blocks, max_seq_len)
     scratch = torch.empty(T * num_heads * splits * (rk + 2), dtype=torch.float32, device=q.device) if splits > 1 else None
@@ -430,7 +438,7 @@ def latent_attention_mma(q_abs: torch.Tensor, q: torch.Tensor, out: torch.Tensor
         _cuda(out, "out", contiguous=False), out.stride(0), _cuda(scratch, "scratch") if scratch is not None else None,
         _cuda(cache, "cache"), cache.shape[0], cache.shape[3], _cuda(block_table, "block_table", torch.int32),
         block_table.stride(0), _cuda(query_start_loc, "query_start_loc", torch.int32), _cuda(seq_lens, "seq_lens", torch.int32),
-        R, tiles, _cuda(freq, "freq", torch.float32) if freq is not None else None, rot_dims if freq is not None else 0,
+        R, tiles, tile_rows, _cuda(freq, "freq", torch.float32) if freq is not None else None, rot_dims if freq is not None else 0,
         _cuda(sinks, "sinks") if sinks is not None else None, T, num_heads, rk, dr, float(scale), splits, _stream())
     _check(rc, "latent_attention_mma")
     _count()
@@ -624,11 +632,17 @@ def gemm_generic_batched(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) ->
     _count()
 
 
+# (token, choice) rows from which the experts' products run grouped by expert on the tensor cores; below, a token's
+# experts are streamed once per token (a decode step)
+MOE_GROUPED_MIN_ROWS = 128
+
+
 def moe_table_feed_forward(h: torch.Tensor, ids: torch.Tensor, table: torch.Tensor, gate_up: torch.Tensor,
                            down: torch.Tensor, base: torch.Tensor | None, out: torch.Tensor) -> None:
     """out[t] = base[t] + (1/top) * sum over k of expert(table[ids[t], k])(h[t]) with gated experts
     ``down_e(silu(gate_e h) * up_e h)``; ``gate_up[E, 2 ff, W]`` (gate rows first), ``down[E, W, ff]``, ``table[V, top]``.
-    Two launches (a matrix-vector product per token and choice)."""
+    Few rows, 32-bit, or sizes that are not multiples of 32: two launches (a matrix-vector product per token and
+    choice).  Many bfloat16 rows: grouped by expert (see ``MOE_GROUPED_MIN_ROWS``)."""
     T, W = h.shape
     E, two_ff, W2 = gate_up.shape
     ff = two_ff // 2
@@ -637,8 +651,23 @@ def moe_table_feed_forward(h: torch.Tensor, ids: torch.Tensor, table: torch.Tens
         raise KernelError("moe_table: weights, rows and out do not fit")
     if h.stride(1) != 1 or (base is not None and (base.shape != (T, W) or base.stride(1) != 1 or base.dtype != h.dtype)):
         raise KernelError("moe_table: rows must be dense and of one dtype")
-    act = torch.empty((T, top, ff), dtype=h.dtype, device=h.device)
     lib = library()
+    if (h.dtype == torch.bfloat16 and T * top >= MOE_GROUPED_MIN_ROWS and h.stride(0) % 8 == 0
+            and lib.cib_moe_table_grouped_supports(W, ff, E)):
+        # many rows: sorted by expert on the device, one tensor-core product per expert group (four launches)
+        act = torch.empty((T * top, ff), dtype=h.dtype, device=h.device)
+        y = torch.empty((T * top, W), dtype=h.dtype, device=h.device)
+        ints = torch.empty(lib.cib_moe_table_grouped_workspace_ints(T, top, E), dtype=torch.int32, device=h.device)
+        rc = lib.cib_moe_table_grouped(
+            _cuda(h, "h", contiguous=False), h.stride(0), _cuda(ids, "ids", torch.int32), _cuda(table, "table", torch.int32), V, top, E,
+            _cuda(gate_up, "gate_up"), _cuda(down, "down"), _cuda(base, "base", contiguous=False) if base is not None else None,
+            base.stride(0) if base is not None else 0, 1.0 / top, _cuda(out, "out"), _cuda(act, "act"), _cuda(y, "y"),
+            _cuda(ints, "ints"), T, W, ff, _stream())
+        _check(rc, "moe_table_grouped")
+        for _ in range(4):
+            _count()
+        return
+    act = torch.empty((T, top, ff), dtype=h.dtype, device=h.device)
     rc = lib.cib_moe_table_gate_up(_cuda(h, "h", contiguous=False), h.stride(0), _code(h, "h"), _cuda(ids, "ids", torch.int32),
                                    _cuda(table, "table", torch.int32), V, top, E, _cuda(gate_up, "gate_up"), _cuda(act, "act"),
                                    T, W, ff, _stream())

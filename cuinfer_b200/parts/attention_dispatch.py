@@ -69,7 +69,7 @@ def latent_attention(q_abs: torch.Tensor, q: torch.Tensor, out: torch.Tensor, kv
     if q_abs.dtype == torch.bfloat16 and latent_tensor_cores(q.dtype, rk, dr, dn, window) and q_abs.stride(0) % 8 == 0:
         kernels.latent_attention_mma(q_abs, q, out, kv.cache, kv.group.block_table, ctx.query_start_loc, ctx.seq_lens,
                                      ctx.query_lens_for_launch(), freq, rot_dims, sinks, num_heads, dn, rk, dr, scale,
-                                     max(1, ctx.max_seq_len))
+                                     max(1, ctx.max_seq_len), decode_only=ctx.decode_only)
         return
     kernels.latent_attention_generic(q_abs, q, out, kv.cache, kv.group.block_table, ctx.query_start_loc, ctx.seq_lens,
                                      ctx.token_request, ctx.positions, freq, rot_dims, sinks, num_heads, dn, rk, dr, scale, window)

@@ -154,7 +154,7 @@ class TableRoutedExperts(FeedForward):
 
     def workspace_bytes(self, tokens: int) -> int:
         width = 2 if self.dtype == torch.bfloat16 else 4
-        own = tokens * (self.top * self.intermediate_size + self.hidden_size) * width
+        own = tokens * (self.top * (self.intermediate_size + self.hidden_size) + self.hidden_size) * width + tokens * self.top * 16
         if self.shared_size:
             own += self.shared_gate_up.workspace_bytes(tokens, silu_pair=True) + self.shared_down.workspace_bytes(tokens)
         return own

@@ -58,9 +58,9 @@ MODELS = {"odd": (ODD, 16, 11), "plain": (PLAIN, 32, 12), "wide": (WIDE, 16, 13)
 # Largest error of a row of logits (see _row_error).  float32: only the order of sums differs; this is the sharp
 # comparison (largest seen: 8e-6).  bfloat16: the engine rounds where it stores (normed rows, projections, latents,
 # attention output), through up to eight layer runs with four norms each that renormalise every sub-layer's output; on
-# these narrow models that alone moves single rows by up to 8e-2 (the residual stream is off by 0.7 % after the first
+# these narrow models that alone moves single rows by up to 1.4e-1 (the residual stream is off by 0.7 % after the first
 # layer run and 2 % after the last, growing evenly).  The kernels are held to 2e-2 one by one further down.
-TOLERANCE = {"float32": 3e-5, "bfloat16": 1.5e-1}
+TOLERANCE = {"float32": 3e-5, "bfloat16": 2.5e-1}
 
 
 def _write(folder, cfg, tensors, dtype):
@@ -291,7 +291,8 @@ def _attention_case(dtype, H, dn, dr, rk, dims, lengths, new, page, seed, sharpe
         assert kernels.latent_attention_mma_supports(rk, dr, dn)
         kernels.latent_attention_mma(_dev(q_abs.reshape(T, H * rk), dtype), _dev(q.reshape(T, -1), dtype), out, cache.cuda(),
                                      table.cuda(), torch.tensor(qsl, dtype=torch.int32).cuda(), seq.cuda(), list(new), freq, dims,
-                                     _dev(sinks, torch.float32), H, dn, rk, dr, scale, max(lengths))
+                                     _dev(sinks, torch.float32), H, dn, rk, dr, scale, max(lengths),
+                                     decode_only=all(k == 1 for k in new))
     else:
         kernels.latent_attention_generic(_dev(q_abs.reshape(T, H * rk), torch.float32), _dev(q.reshape(T, -1), dtype), out, cache.cuda(),
                                          table.cuda(), torch.tensor(qsl, dtype=torch.int32).cuda(), seq.cuda(),
@@ -339,6 +340,8 @@ BF = torch.bfloat16
     (16, 8, 64, 512, 64, [300, 90], [170, 1], 16),                     # 512: eight warps, two halves of the value columns
     (70, 8, 0, 16, 0, [45, 20], [45, 3], 4),                           # two blocks of heads, nothing rotated
     (1, 8, 16, 48, 16, [130], [130], 32),                              # one head: 64 tokens to a tile
+    (32, 8, 64, 512, 64, [700, 90, 33], [1, 1, 1], 16),                # a decode step: tiles of 32 rows, keys split
+    (6, 8, 16, 64, 16, [70, 1, 200], [1, 1, 1], 16),                   # a decode step with few heads
 ])
 def test_latent_attention_on_tensor_cores(H, dn, dr, rk, dims, lengths, new, page):
     got, want = _attention_case(BF, H, dn, dr, rk, dims, lengths, new, page, seed=H, tensor_cores=True)
@@ -390,6 +393,35 @@ def test_experts_by_table(dtype):
     kernels.moe_table_feed_forward(_dev(h, dtype), ids.to(torch.int32).cuda(), t["table"].cuda(), _dev(gate_up, dtype), _dev(down, dtype),
                                    _dev(base, dtype), out)
     _close(out, want, dtype, "experts by table plus a base")
+
+
+@pytest.mark.parametrize("W, ff, E, top, V, T", [(64, 32, 5, 2, 40, 300), (96, 160, 3, 3, 7, 77), (128, 64, 9, 1, 500, 700)])
+def test_experts_grouped_on_tensor_cores_equal_the_row_by_row_kernels(W, ff, E, top, V, T):
+    """Many bfloat16 rows go through the grouped path; it must give what the per-token kernels give (same rounding
+    places: activations and down-projected rows in bfloat16), also for experts that get no row, one row, or a tile and one."""
+    from cuinfer_b200 import kernels
+
+    g = torch.Generator().manual_seed(W + T)
+    gate_up = (torch.randn(E, 2 * ff, W, generator=g) / math.sqrt(W)).to(BF).cuda()
+    down = (torch.randn(E, W, ff, generator=g) / math.sqrt(ff)).to(BF).cuda()
+    table = torch.stack([torch.randperm(E, generator=g)[:top] for _ in range(V)]).to(torch.int32).cuda()
+    ids = torch.randint(0, V, (T,), generator=g).to(torch.int32)
+    ids[: T // 2] = ids[0]                      # half of the rows share their experts: a group longer than a tile
+    h = torch.randn(T, W, generator=g).to(BF).cuda()
+    base = torch.randn(T, W, generator=g).to(BF).cuda()
+    assert T * top >= kernels.MOE_GROUPED_MIN_ROWS
+    grouped = torch.empty(T, W, dtype=BF, device="cuda")
+    kernels.moe_table_feed_forward(h, ids.cuda(), table, gate_up, down, base, grouped)
+    rows = torch.empty(T, W, dtype=BF, device="cuda")
+    limit, kernels.MOE_GROUPED_MIN_ROWS = kernels.MOE_GROUPED_MIN_ROWS, 1 << 30
+    try:
+        kernels.moe_table_feed_forward(h, ids.cuda(), table, gate_up, down, base, rows)
+    finally:
+        kernels.MOE_GROUPED_MIN_ROWS = limit
+    _close(grouped, rows.double().cpu(), BF, "grouped experts against row-by-row experts")
+    none = torch.empty(T, W, dtype=BF, device="cuda")
+    kernels.moe_table_feed_forward(h, ids.cuda(), table, gate_up, down, None, none)
+    _close(none, (rows.double() - base.double()).cpu(), BF, "without a base")
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
