@@ -177,6 +177,38 @@ def test_greedy_generation_through_the_entry_point(folders):
             assert out.token_ids == plain.greedy(cfg, tensors, prompt, 12), f"{name}: prompt of {len(prompt)} tokens"
 
 
+def test_command_line_and_sampling(folders, tmp_path):
+    """The command line builds the design from a folder and from a bare configuration with random weights; sampled
+    tokens (temperature, top-k, top-p) do not depend on how the engine batches."""
+    import subprocess
+    import sys
+
+    from conftest import ROOT
+    from cuinfer_b200 import LLM, SamplingParams
+
+    cfg, dirs, tensors, block = folders["plain"]
+    prompt = random_tokens(cfg["vocab"], 9, 95)
+    proc = subprocess.run([sys.executable, "-m", "cuinfer_b200", "generate", "--model", dirs["float32"], "--dtype", "float32",
+                           "--prompt-ids", ",".join(map(str, prompt)), "--max-tokens", "5", "--temperature", "0", "--ignore-eos",
+                           "--num-blocks", "16", "--max-num-seqs", "4", "--block-size", str(block)],
+                          capture_output=True, text=True, cwd=ROOT, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    line = [json.loads(l) for l in proc.stdout.splitlines() if l.startswith("{")][0]
+    assert line["token_ids"] == plain.greedy(cfg, tensors, prompt, 5)
+    path = tmp_path / "config.json"
+    path.write_text(json.dumps(MODELS["odd"][0]))
+    proc = subprocess.run([sys.executable, "-m", "cuinfer_b200", "generate", "--random-config", str(path), "--seed", "3",
+                           "--prompt-ids", "1 2 3", "--max-tokens", "4", "--num-blocks", "16", "--max-num-seqs", "2"],
+                          capture_output=True, text=True, cwd=ROOT, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert len([json.loads(l) for l in proc.stdout.splitlines() if l.startswith("{")][0]["token_ids"]) == 4
+    prompts = [random_tokens(cfg["vocab"], n, 40 + n) for n in (5, 21, 12, 30)]
+    params = SamplingParams(max_tokens=10, temperature=0.8, top_k=20, top_p=0.9, ignore_eos=True)
+    a = LLM(dirs["float32"], dtype="float32", block_size=block, num_blocks=24, max_num_seqs=4, max_num_scheduled_tokens=16, seed=1)
+    b = LLM(dirs["float32"], dtype="float32", block_size=block, num_blocks=24, max_num_seqs=2, max_num_scheduled_tokens=512, seed=1)
+    assert [o.token_ids for o in a.generate(prompts, params)] == [o.token_ids for o in b.generate(prompts, params)]
+
+
 # ---- mechanisms alone -------------------------------------------------------------------------------------------------
 def _dev(t, dtype):
     return t.to(device="cuda", dtype=dtype).contiguous()
