@@ -40,7 +40,10 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_abs, int qa_stri
     const int splits = gridDim.z, split = blockIdx.z;
 
     if (tid == 0) {
-        int t = blockIdx.x, r = 0;
+        // The last CTAs of the grid take the first tiles: a request's late tokens see the most keys, and the tiles that
+        // run longest should start first.  (A captured step's grid is an upper bound; the CTAs beyond the batch's own
+        // tiles are then the FIRST to be scheduled, find no request and leave.)
+        int t = gridDim.x - 1 - blockIdx.x, r = 0;
         for (; r < num_requests; ++r) {
             const int tiles = (query_start_loc[r + 1] - query_start_loc[r] + TM - 1) / TM;
             if (t < tiles) break;
@@ -164,18 +167,31 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_abs, int qa_stri
             const int arow = rg * 16 + (mat & 1) * 8 + rr;
             const uint32_t a_base = smem_u32(sQ + arow * LD + (mat >> 1) * 8);
             const uint32_t b_base = smem_u32(sKt + ((mat >> 1) * 8 + rr) * LD + (mat & 1) * 8);
-#pragma unroll 4
-            for (int kt = 0; kt < D / 16; ++kt) {
-                uint32_t a[4];
+            // fragments of step kt + 1 are asked for before the products of step kt are issued: with two warps to a
+            // scheduler nothing else hides the shared-memory latency
+            const int ksteps = D / 16;
+            uint32_t a0[4], a1[4], b0[kLmN / 16][4], b1[kLmN / 16][4];
+            auto fetch = [&](uint32_t (&a)[4], uint32_t (&b)[kLmN / 16][4], int kt) {
                 ldmatrix_x4(a, a_base + kt * 32);
 #pragma unroll
+                for (int np = 0; np < kLmN / 16; ++np) ldmatrix_x4(b[np], b_base + (np * 16 * LD + kt * 16) * 2);
+            };
+            auto multiply = [&](const uint32_t (&a)[4], const uint32_t (&b)[kLmN / 16][4]) {
+#pragma unroll
                 for (int np = 0; np < kLmN / 16; ++np) {
-                    uint32_t b[4];
-                    ldmatrix_x4(b, b_base + (np * 16 * LD + kt * 16) * 2);
-                    mma_bf16_16816(s[2 * np], a, b[0], b[1]);
-                    mma_bf16_16816(s[2 * np + 1], a, b[2], b[3]);
+                    mma_bf16_16816(s[2 * np], a, b[np][0], b[np][1]);
+                    mma_bf16_16816(s[2 * np + 1], a, b[np][2], b[np][3]);
                 }
+            };
+            fetch(a0, b0, 0);
+            int kt = 0;
+            for (; kt + 1 < ksteps; kt += 2) {
+                fetch(a1, b1, kt + 1);
+                multiply(a0, b0);
+                if (kt + 2 < ksteps) fetch(a0, b0, kt + 2);
+                multiply(a1, b1);
             }
+            if (kt < ksteps) multiply(a0, b0);
         }
         // ---- scale, causal mask where the tile touches the diagonal, running maximum ----
         const bool need_mask = key0 + kLmN - 1 > warp_pos_min;

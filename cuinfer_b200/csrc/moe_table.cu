@@ -21,6 +21,46 @@ __device__ __forceinline__ float dot_row(const T* __restrict__ w, const float* _
     for (int i = lane; i < n; i += 32) s = fmaf(to_f32(w[i]), x[i], s);
     return warp_sum(s);
 }
+// bfloat16 rows of a multiple of 8 values that start on a 16-byte boundary: a lane reads 16 bytes at a time (a warp
+// 512 bytes per load instead of 64), four loads issued before the first is used.
+template <>
+__device__ __forceinline__ float dot_row<__nv_bfloat16>(const __nv_bfloat16* __restrict__ w, const float* __restrict__ x, int n,
+                                                        int lane) {
+    float s = 0.f;
+    if ((n & 7) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
+        const uint4* w8 = reinterpret_cast<const uint4*>(w);
+        const int chunks = n >> 3;
+        int c = lane;
+        for (; c + 96 < chunks; c += 128) {
+            uint4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] = __ldg(w8 + c + 32 * u);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[u]);
+                const float* xs = x + (c + 32 * u) * 8;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    s = fmaf(__low2float(h[k]), xs[2 * k], s);
+                    s = fmaf(__high2float(h[k]), xs[2 * k + 1], s);
+                }
+            }
+        }
+        for (; c < chunks; c += 32) {
+            const uint4 v = __ldg(w8 + c);
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+            const float* xs = x + c * 8;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                s = fmaf(__low2float(h[k]), xs[2 * k], s);
+                s = fmaf(__high2float(h[k]), xs[2 * k + 1], s);
+            }
+        }
+    } else {
+        for (int i = lane; i < n; i += 32) s = fmaf(__bfloat162float(w[i]), x[i], s);
+    }
+    return warp_sum(s);
+}
 
 template <typename T>
 __global__ void __launch_bounds__(kMoeWarps * 32)
