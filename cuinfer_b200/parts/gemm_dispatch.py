@@ -27,6 +27,10 @@ import os
 
 from .. import kernels
 
+# The library products of this package accumulate in 32 bits throughout: cuBLAS may otherwise reduce the partial sums
+# of a split-K product in bfloat16 (torch allows that by default).
+torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+
 TCGEN05_MIN_ROWS = 128
 TCGEN05_MIN_TILES = 296          # output tiles of 128 x 128 from which the tcgen05 kernel is chosen over the library
 FEW_ROWS = 16

@@ -30,6 +30,7 @@ import torch
 
 from .. import kernels
 from . import attention_dispatch
+from . import gemm_dispatch  # noqa: F401  (sets the library products to 32-bit accumulation before the first one runs)
 from .base import Mixer
 from .context import StepContext
 from .linear import Linear
