@@ -34,9 +34,10 @@ class CacheGroupSpec:
     head_dim: int
     window: Optional[int] = None      # None: every token is kept
     planes: int = 2                   # rows of head_dim a head keeps per token: keys and values, or one shared row
+    keep_first: int = 0               # with a window: the first so many tokens stay visible, so their pages stay held
 
     def key(self) -> tuple:
-        return (self.num_kv_heads, self.head_dim, self.window, self.planes)
+        return (self.num_kv_heads, self.head_dim, self.window, self.planes, self.keep_first)
 
 
 class PagePool:
@@ -225,7 +226,8 @@ class CacheManager:
             first_page = first_needed // self.page_size
             table = held.tables[g]
             gone = []
-            for idx in range(held.first_live[g], min(first_page, len(table))):
+            kept_pages = self._pages_for(spec.keep_first) if spec.keep_first > 0 else 0    # pages of the tokens that stay visible
+            for idx in range(max(held.first_live[g], kept_pages), min(first_page, len(table))):
                 if table[idx] >= 0:
                     gone.append(table[idx])
                     table[idx] = -1
@@ -280,9 +282,10 @@ class CacheManager:
 
 
 def group_runs(needs: Dict[int, "object"]) -> List[CacheGroupSpec]:
-    """Group runs by (kv heads, head size, window, planes): runs with equal needs share pages ids and tables."""
+    """Group runs by (kv heads, head size, window, planes, kept first tokens): runs with equal needs share pages ids and tables."""
     by_key: Dict[tuple, List[int]] = {}
     for run in sorted(needs):
         n = needs[run]
-        by_key.setdefault((n.num_kv_heads, n.head_dim, n.window, getattr(n, "planes", 2)), []).append(run)
-    return [CacheGroupSpec(tuple(runs), k[0], k[1], k[2], k[3]) for k, runs in by_key.items()]
+        keep = getattr(n, "keep_first", 0) if n.window is not None else 0
+        by_key.setdefault((n.num_kv_heads, n.head_dim, n.window, getattr(n, "planes", 2), keep), []).append(run)
+    return [CacheGroupSpec(tuple(runs), k[0], k[1], k[2], k[3], k[4]) for k, runs in by_key.items()]

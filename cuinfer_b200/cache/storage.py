@@ -38,16 +38,32 @@ class CacheStorage:
             for i, run in enumerate(spec.runs):
                 self.run_cache[run] = pool[i]
                 self.run_group[run] = g
-        self.state: Dict[int, torch.Tensor] = {}
-        for run, need in state_needs.items():
+        self.state: Dict[int, object] = {}          # run -> tensor, or name -> tensor for a mixer with several
+
+        def make(need: StateNeed) -> torch.Tensor:
             if need.dtype not in _STATE_DTYPES:
                 raise ValueError(f"state dtype {need.dtype!r} is not one of {sorted(_STATE_DTYPES)}")
-            self.state[run] = torch.zeros((max_requests, *need.shape), dtype=_STATE_DTYPES[need.dtype], device=device)
+            return torch.zeros((max_requests, *need.shape), dtype=_STATE_DTYPES[need.dtype], device=device)
+
+        for run, need in state_needs.items():
+            if isinstance(need, (tuple, list)):
+                if len({n.name for n in need}) != len(need) or not all(n.name for n in need):
+                    raise ValueError(f"run {run}: several state tensors need a name each")
+                self.state[run] = {n.name: make(n) for n in need}
+            else:
+                self.state[run] = make(need)
+
+    def state_tensors(self) -> List[torch.Tensor]:
+        out: List[torch.Tensor] = []
+        for entry in self.state.values():
+            out.extend(entry.values() if isinstance(entry, dict) else [entry])
+        return out
 
     def zero_slots(self, slots: Sequence[int]) -> None:
         """A request that has just been admitted starts from zero state."""
-        if not slots or not self.state:
+        tensors = self.state_tensors()
+        if not slots or not tensors:
             return
-        idx = torch.tensor(list(slots), dtype=torch.long, device=next(iter(self.state.values())).device)
-        for t in self.state.values():
+        idx = torch.tensor(list(slots), dtype=torch.long, device=tensors[0].device)
+        for t in tensors:
             t.index_fill_(0, idx, 0)

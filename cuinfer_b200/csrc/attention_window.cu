@@ -1,0 +1,212 @@
+// Grouped-query attention whose keys and values have sizes of their own, with a capped score and a window that keeps
+// the first tokens of a sequence visible: the step before the attention (rotation, unit norm, value mixing, cache write)
+// and the plain all-sizes attention kernel (a warp per query token and head), which is the 32-bit path.
+//
+// Per token and head, with the query q and key k of d values and the value v of dv values:
+//   rotation of the first `rot_dims` values in neighbouring pairs (2i, 2i+1) by the angle pos * freq[i] (32-bit angle,
+//   full-range sine and cosine), then q and k divided by their root mean square (eps inside the root), no gain;
+//   v = (1 - lambda) * v + lambda * v_first for a layer that mixes in an earlier layer's values of the same token;
+//   score = scale * q.k, then cap * tanh(score / cap) if cap > 0;
+//   query at position i sees key j when j <= i and (window == 0 or i - j < window or j < keep_first);
+//   softmax over the visible keys, weighted sum of their values.
+// Everything after the loads is 32-bit; exponentials, tangents, sines are the exact ones.
+//
+// Cache layout of one layer run: [page][kv head][slot in page][d + dv] — a token's key and value side by side.
+#include "common.cuh"
+
+namespace cib {
+
+constexpr int kPrepWarps = 8;
+constexpr int kPrepMaxPairsPerLane = 8;      // d and dv up to 512
+
+// One warp per (token, vector): H query heads, G key heads, G value heads of the packed rows [q | k | v].
+template <typename T>
+__global__ void __launch_bounds__(kPrepWarps * 32)
+window_attention_prep_kernel(T* __restrict__ qkv, int stride, const int* __restrict__ positions,
+                             const int* __restrict__ slot_mapping, const float* __restrict__ freq, int rot_dims, float eps,
+                             int H, int G, int d, int dv, const T* __restrict__ v_first, int v_first_stride,
+                             AnyVec lambda, int has_lambda, T* __restrict__ cache, long long num_slots, int page_size,
+                             int num_tokens) {
+    const int lane = threadIdx.x & 31;
+    const int vectors = H + 2 * G;
+    const long long w = (long long)blockIdx.x * kPrepWarps + (threadIdx.x >> 5);
+    if (w >= (long long)num_tokens * vectors) return;
+    const int t = (int)(w / vectors), vec = (int)(w % vectors);
+    T* row = qkv + (size_t)t * stride;
+    const int slot = slot_mapping ? slot_mapping[t] : -1;
+    const bool store = cache && slot >= 0 && slot < num_slots;
+    const int width = d + dv;
+    if (vec >= H + G) {                                   // a value head: mix and store
+        const int g = vec - H - G;
+        if (!store) return;
+        const T* v = row + (size_t)H * d + (size_t)G * d + (size_t)g * dv;
+        const float lam = has_lambda ? lambda[0] : 0.f;
+        T* dst = cache + (((size_t)(slot / page_size) * G + g) * page_size + slot % page_size) * width + d;
+        for (int i = lane; i < dv; i += 32) {
+            float x = to_f32(v[i]);
+            if (has_lambda) x = (1.f - lam) * x + lam * to_f32(v_first[(size_t)t * v_first_stride + (size_t)g * dv + i]);
+            dst[i] = from_f32<T>(x);
+        }
+        return;
+    }
+    const bool is_key = vec >= H;
+    T* x = is_key ? row + (size_t)H * d + (size_t)(vec - H) * d : row + (size_t)vec * d;
+    const float pos = (float)positions[t];
+    float a[kPrepMaxPairsPerLane], b[kPrepMaxPairsPerLane];
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < kPrepMaxPairsPerLane; ++c) {
+        const int p = c * 32 + lane, e = 2 * p;
+        a[c] = e < d ? to_f32(x[e]) : 0.f;
+        b[c] = e + 1 < d ? to_f32(x[e + 1]) : 0.f;
+        if (e + 1 < rot_dims && e + 1 < d) {
+            float sn, cs;
+            sincosf(pos * freq[p], &sn, &cs);
+            const float u = a[c], v = b[c];
+            a[c] = u * cs - v * sn;
+            b[c] = v * cs + u * sn;
+        }
+        ss += a[c] * a[c] + b[c] * b[c];
+    }
+    ss = warp_sum(ss);
+    const float factor = 1.f / sqrtf(ss / (float)d + eps);
+    T* dst = x;
+    if (is_key) {
+        if (!store) return;
+        dst = cache + (((size_t)(slot / page_size) * G + (vec - H)) * page_size + slot % page_size) * width;
+    }
+#pragma unroll
+    for (int c = 0; c < kPrepMaxPairsPerLane; ++c) {
+        const int e = 2 * (c * 32 + lane);
+        if (e < d) dst[e] = from_f32<T>(a[c] * factor);
+        if (e + 1 < d) dst[e + 1] = from_f32<T>(b[c] * factor);
+    }
+}
+
+constexpr int kWinWarps = 4;
+constexpr int kWinMaxAcc = 16;               // dv up to 512
+
+template <typename T>
+__global__ void __launch_bounds__(kWinWarps * 32)
+window_attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, int out_stride,
+                                const T* __restrict__ cache, int num_pages, int page_size,
+                                const int* __restrict__ block_table, int table_stride, const int* __restrict__ positions,
+                                const int* __restrict__ token_request, int H, int G, int d, int dv, float scale, float cap,
+                                int window, int keep_first) {
+    extern __shared__ float smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x;
+    const int head = blockIdx.y * kWinWarps + warp;
+    if (head >= H) return;
+    const int g = head / (H / G);
+    float* qs = smem + warp * d;
+    const int r = token_request[t];
+    const int pos = positions[t];
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int kept = window > 0 ? min(keep_first, lo) : 0;        // keys 0..kept-1 lie before the window and stay visible
+    const int* table = block_table + (size_t)r * table_stride;
+    const T* qp = q + (size_t)t * q_stride + (size_t)head * d;
+    for (int i = lane; i < d; i += 32) qs[i] = to_f32(qp[i]);
+    __syncwarp();
+
+    float acc[kWinMaxAcc];
+#pragma unroll
+    for (int k = 0; k < kWinMaxAcc; ++k) acc[k] = 0.f;
+    float m = -INFINITY, l = 0.f;
+    const int width = d + dv;
+    const float inv_cap = cap > 0.f ? 1.f / cap : 0.f;
+
+    for (int seg = 0; seg < 2; ++seg) {
+        const int begin = seg == 0 ? 0 : lo, end = seg == 0 ? kept : pos + 1;
+        for (int c = begin; c < end; c += 32) {
+            const int j = c + lane;
+            float s = -INFINITY;
+            const T* row = nullptr;
+            if (j < end) {
+                const int page = table[j / page_size];
+                if (page >= 0 && page < num_pages) {
+                    row = cache + (((size_t)page * G + g) * page_size + j % page_size) * width;
+                    float dot = 0.f;
+                    for (int i = 0; i < d; ++i) dot = fmaf(qs[i], to_f32(row[i]), dot);
+                    s = dot * scale;
+                    if (cap > 0.f) s = cap * tanhf(s * inv_cap);
+                }
+            }
+            const float m_new = fmaxf(m, warp_max(s));
+            if (m_new == -INFINITY) continue;                     // nothing visible in this chunk
+            const float p = s == -INFINITY ? 0.f : expf(s - m_new);
+            const float corr = m == -INFINITY ? 0.f : expf(m - m_new);
+            l = l * corr + warp_sum(p);
+            m = m_new;
+#pragma unroll
+            for (int k = 0; k < kWinMaxAcc; ++k) acc[k] *= corr;
+            const int count = min(32, end - c);
+            for (int jj = 0; jj < count; ++jj) {
+                const float pj = __shfl_sync(0xffffffffu, p, jj);
+                const T* vj = reinterpret_cast<const T*>(__shfl_sync(0xffffffffu, reinterpret_cast<uintptr_t>(row), jj));
+                if (pj == 0.f || vj == nullptr) continue;
+#pragma unroll
+                for (int k = 0; k < kWinMaxAcc; ++k) {
+                    const int i = k * 32 + lane;
+                    if (i < dv) acc[k] = fmaf(pj, to_f32(vj[d + i]), acc[k]);
+                }
+            }
+        }
+    }
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    T* op = out + (size_t)t * out_stride + (size_t)head * dv;
+#pragma unroll
+    for (int k = 0; k < kWinMaxAcc; ++k) {
+        const int i = k * 32 + lane;
+        if (i < dv) op[i] = from_f32<T>(acc[k] * inv);
+    }
+}
+
+}  // namespace cib
+
+using namespace cib;
+
+extern "C" int cib_window_attention_prep(void* qkv, int dtype, int stride, const int* positions, const int* slot_mapping,
+                                         const float* freq, int rot_dims, float eps, int H, int G, int d, int dv,
+                                         const void* v_first, int v_first_stride, const void* lambda, int lambda_dtype,
+                                         void* cache, long long num_slots, int page_size, int num_tokens,
+                                         cudaStream_t stream) {
+    CIB_REQUIRE(H > 0 && G > 0 && H % G == 0 && d > 0 && dv > 0, "window_attention_prep: bad head counts or sizes");
+    CIB_REQUIRE(d <= 64 * kPrepMaxPairsPerLane, "window_attention_prep: head size %d is beyond %d", d, 64 * kPrepMaxPairsPerLane);
+    CIB_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= d && (rot_dims == 0 || freq), "window_attention_prep: bad rotation");
+    CIB_REQUIRE((v_first == nullptr) == (lambda == nullptr), "window_attention_prep: mixing needs both the values and the factor");
+    if (num_tokens == 0) return 0;
+    const long long warps = (long long)num_tokens * (H + 2 * G);
+    const int blocks = (int)((warps + kPrepWarps - 1) / kPrepWarps);
+    AnyVec lam{lambda, lambda_dtype == kBF16};
+    if (dtype == kF32)
+        window_attention_prep_kernel<float><<<blocks, kPrepWarps * 32, 0, stream>>>((float*)qkv, stride, positions, slot_mapping, freq, rot_dims, eps, H, G, d, dv, (const float*)v_first, v_first_stride, lam, lambda != nullptr, (float*)cache, num_slots, page_size, num_tokens);
+    else if (dtype == kBF16)
+        window_attention_prep_kernel<__nv_bfloat16><<<blocks, kPrepWarps * 32, 0, stream>>>((__nv_bfloat16*)qkv, stride, positions, slot_mapping, freq, rot_dims, eps, H, G, d, dv, (const __nv_bfloat16*)v_first, v_first_stride, lam, lambda != nullptr, (__nv_bfloat16*)cache, num_slots, page_size, num_tokens);
+    else
+        CIB_REQUIRE(false, "window_attention_prep: bad dtype %d", dtype);
+    CIB_LAUNCH_CHECK("window_attention_prep");
+    return 0;
+}
+
+extern "C" int cib_window_attention_generic(const void* q, int dtype, int q_stride, void* out, int out_stride, const void* cache,
+                                            int num_pages, int page_size, const int* block_table, int table_stride,
+                                            const int* positions, const int* token_request, int num_tokens, int H, int G,
+                                            int d, int dv, float scale, float cap, int window, int keep_first,
+                                            cudaStream_t stream) {
+    CIB_REQUIRE(H > 0 && G > 0 && H % G == 0 && d > 0 && dv > 0, "window_attention: bad head counts or sizes");
+    CIB_REQUIRE(dv <= 32 * kWinMaxAcc, "window_attention: value size %d is beyond %d", dv, 32 * kWinMaxAcc);
+    CIB_REQUIRE(d <= 2048, "window_attention: head size %d is beyond 2048", d);
+    CIB_REQUIRE(window >= 0 && keep_first >= 0, "window_attention: bad window");
+    if (num_tokens == 0) return 0;
+    dim3 grid(num_tokens, (H + kWinWarps - 1) / kWinWarps);
+    const size_t smem = (size_t)kWinWarps * d * sizeof(float);
+    if (dtype == kF32)
+        window_attention_generic_kernel<float><<<grid, kWinWarps * 32, smem, stream>>>((const float*)q, q_stride, (float*)out, out_stride, (const float*)cache, num_pages, page_size, block_table, table_stride, positions, token_request, H, G, d, dv, scale, cap, window, keep_first);
+    else if (dtype == kBF16)
+        window_attention_generic_kernel<__nv_bfloat16><<<grid, kWinWarps * 32, smem, stream>>>((const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)cache, num_pages, page_size, block_table, table_stride, positions, token_request, H, G, d, dv, scale, cap, window, keep_first);
+    else
+        CIB_REQUIRE(false, "window_attention: bad dtype %d", dtype);
+    CIB_LAUNCH_CHECK("window_attention_generic");
+    return 0;
+}

@@ -5,6 +5,8 @@
 // csrc/ops/residual_rms_norm_fused.cu:26-110, csrc/ops/residual_add.cu:23-82, csrc/ops/swiglu.cu:34-60.
 // Unlike those, every size is a run-time parameter, the residual stream is kept in 32 bits, and the
 // add, the norm and the store of the new residual are one pass over the row.
+#include <algorithm>
+
 #include "common.cuh"
 #include "mma_utils.cuh"
 
@@ -346,5 +348,107 @@ extern "C" int cib_silu_mul(const void* gate_up, void* act, int dtype, int rows,
         CIB_REQUIRE(false, "silu_mul: unsupported dtype %d", dtype);
     }
     CIB_LAUNCH_CHECK("silu_mul");
+    return 0;
+}
+
+// ---- RMS norms on both sides of the residual sum ---------------------------------------------------------------------
+// One pass over a 32-bit residual row x with an outstanding delta y (either may be absent):
+//   x += post ? y * rsqrt(mean(y^2) + post_eps) * post_gain : y          (a sub-layer's output, normed before it is added)
+//   raw  = x rounded to the rows' type                                   (for a part that reads the stream itself)
+//   out  = x * rsqrt(mean(x^2) + eps) * gain                             (the next sub-layer's input)
+// Statistics 32-bit; a block per row, the row staged in shared memory.
+namespace cib {
+
+template <typename TD, typename TO>
+__global__ void __launch_bounds__(256)
+rms_stream_kernel(float* __restrict__ residual, const TD* __restrict__ delta, AnyVec post_gain, int has_post, float post_eps,
+                  AnyVec gain, float eps, TO* __restrict__ out, TO* __restrict__ raw, int hidden) {
+    extern __shared__ float row_s[];
+    __shared__ float scratch[33];
+    const size_t row = (size_t)blockIdx.x * hidden;
+    float factor = 1.f;
+    if (delta && has_post) {
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+            const float y = to_f32(delta[row + i]);
+            ss = fmaf(y, y, ss);
+        }
+        ss = block_sum(ss, scratch);
+        factor = 1.f / sqrtf(ss / (float)hidden + post_eps);
+    }
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float x = residual[row + i];
+        if (delta) {
+            const float y = to_f32(delta[row + i]);
+            x += has_post ? y * factor * post_gain[i] : y;
+            residual[row + i] = x;
+        }
+        row_s[i] = x;
+        ss = fmaf(x, x, ss);
+        if (raw) raw[row + i] = from_f32<TO>(x);
+    }
+    if (!out) return;
+    ss = block_sum(ss, scratch);
+    const float f2 = 1.f / sqrtf(ss / (float)hidden + eps);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[row + i] = from_f32<TO>(row_s[i] * f2 * gain[i]);
+}
+
+// out[t, j] = gelu_tanh(x[t, j]) (* table[ids[t], j] when a table is given);
+// gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))), 32-bit with the exact tangent.
+template <typename T>
+__global__ void gelu_tanh_kernel(const T* __restrict__ x, const T* __restrict__ table, int table_stride,
+                                 const int* __restrict__ ids, int vocab, T* __restrict__ out, int cols, long long total) {
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+        const float z = to_f32(x[e]);
+        float y = 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+        if (table) {
+            const long long t = e / cols;
+            const int id = ids[t];
+            y = (id >= 0 && id < vocab) ? y * to_f32(table[(size_t)id * table_stride + (e - t * cols)]) : 0.f;
+        }
+        out[e] = from_f32<T>(y);
+    }
+}
+
+}  // namespace cib
+
+extern "C" int cib_rms_stream(float* residual, const void* delta, int delta_dtype, const void* post_gain, int post_dtype,
+                              float post_eps, const void* gain, int gain_dtype, float eps, void* out, void* raw,
+                              int out_dtype, int rows, int hidden, cudaStream_t stream) {
+    using namespace cib;
+    CIB_REQUIRE(rows >= 0 && hidden > 0 && hidden <= 12 * 1024, "rms_stream: bad sizes (%d x %d)", rows, hidden);
+    CIB_REQUIRE(!post_gain || delta, "rms_stream: an output norm needs rows to norm");
+    CIB_REQUIRE(!out || gain, "rms_stream: out needs the norm's gain");
+    if (rows == 0) return 0;
+    AnyVec pg{post_gain, post_dtype == kBF16}, g{gain, gain_dtype == kBF16};
+    const size_t smem = (size_t)hidden * sizeof(float);
+    const int has_post = post_gain != nullptr;
+#define CIB_RMS_STREAM(TD, TO) \
+    rms_stream_kernel<TD, TO><<<rows, 256, smem, stream>>>(residual, (const TD*)delta, pg, has_post, post_eps, g, eps, (TO*)out, (TO*)raw, hidden)
+    const bool d16 = delta && delta_dtype == kBF16, o16 = out_dtype == kBF16;
+    if (d16 && o16) CIB_RMS_STREAM(__nv_bfloat16, __nv_bfloat16);
+    else if (d16) CIB_RMS_STREAM(__nv_bfloat16, float);
+    else if (o16) CIB_RMS_STREAM(float, __nv_bfloat16);
+    else CIB_RMS_STREAM(float, float);
+#undef CIB_RMS_STREAM
+    CIB_LAUNCH_CHECK("rms_stream");
+    return 0;
+}
+
+extern "C" int cib_gelu_tanh(const void* x, const void* table, int table_stride, const int* ids, int vocab, void* out, int dtype,
+                             int rows, int cols, cudaStream_t stream) {
+    using namespace cib;
+    CIB_REQUIRE(rows >= 0 && cols > 0 && (!table || ids), "gelu_tanh: bad arguments");
+    const long long total = (long long)rows * cols;
+    if (total == 0) return 0;
+    const int blocks = (int)std::min<long long>((total + 255) / 256, 148 * 16);
+    if (dtype == kF32)
+        gelu_tanh_kernel<float><<<blocks, 256, 0, stream>>>((const float*)x, (const float*)table, table_stride, ids, vocab, (float*)out, cols, total);
+    else if (dtype == kBF16)
+        gelu_tanh_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)table, table_stride, ids, vocab, (__nv_bfloat16*)out, cols, total);
+    else
+        CIB_REQUIRE(false, "gelu_tanh: bad dtype %d", dtype);
+    CIB_LAUNCH_CHECK("gelu_tanh");
     return 0;
 }

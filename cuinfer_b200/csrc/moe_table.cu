@@ -8,12 +8,30 @@
 // Dots and the gate are 32-bit with the exact exponential; act and out are rounded once to the rows' type.
 // Weights: gate_up [E][2 ff][W] (gate rows, then up rows), down [E][W][ff].  A table entry outside 0..E-1 contributes
 // nothing.  `base` (another feed-forward's output, a shared expert's say) may be null.
+//
+// The same kernels serve experts chosen by a router: `ids` null means that the table is indexed by the row itself
+// (table[t][k] = the k-th expert chosen for row t), `weights[t][k]` (32-bit, may be null) replaces the uniform weight,
+// and `act_kind` 1 selects the clamped gate  g = min(gate, limit), u = clamp(up, -limit, limit),
+// act = g * sigmoid(1.702 g) * (u + 1)  instead of silu(gate) * up.
 #include "common.cuh"
 
 namespace cib {
 
 constexpr int kMoeWarps = 8;
 constexpr int kMoeOutsPerBlock = 64;
+
+struct ExpertAct {
+    int kind;        // 0: silu(gate) * up;  1: the clamped gate described above
+    float limit;
+    __device__ __forceinline__ float operator()(float g, float u) const {
+        if (kind == 1) {
+            g = fminf(g, limit);
+            u = fminf(fmaxf(u, -limit), limit);
+            return g / (1.f + expf(-1.702f * g)) * (u + 1.f);
+        }
+        return g / (1.f + expf(-g)) * u;
+    }
+};
 
 template <typename T>
 __device__ __forceinline__ float dot_row(const T* __restrict__ w, const float* __restrict__ x, int n, int lane) {
@@ -66,13 +84,13 @@ template <typename T>
 __global__ void __launch_bounds__(kMoeWarps * 32)
 moe_table_gate_up_kernel(const T* __restrict__ h, int h_stride, const int* __restrict__ ids,
                          const int* __restrict__ table, int vocab, int top, int experts,
-                         const T* __restrict__ gate_up, T* __restrict__ act, int width, int ff) {
+                         const T* __restrict__ gate_up, T* __restrict__ act, int width, int ff, ExpertAct fn) {
     extern __shared__ float hs[];
     const int t = blockIdx.x / top, k = blockIdx.x % top;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int i = threadIdx.x; i < width; i += blockDim.x) hs[i] = to_f32(h[(size_t)t * h_stride + i]);
     __syncthreads();
-    const int id = ids[t];
+    const int id = ids ? ids[t] : t;
     const int e = (id >= 0 && id < vocab) ? table[(size_t)id * top + k] : -1;
     const bool ok = e >= 0 && e < experts;
     const T* wg = gate_up + (size_t)(ok ? e : 0) * 2 * ff * width;
@@ -83,7 +101,7 @@ moe_table_gate_up_kernel(const T* __restrict__ h, int h_stride, const int* __res
         if (ok) {
             const float g = dot_row(wg + (size_t)j * width, hs, width, lane);
             const float u = dot_row(wu + (size_t)j * width, hs, width, lane);
-            v = g / (1.f + expf(-g)) * u;
+            v = fn(g, u);
         }
         if (lane == 0) act[((size_t)t * top + k) * ff + j] = from_f32<T>(v);
     }
@@ -93,13 +111,13 @@ template <typename T>
 __global__ void __launch_bounds__(kMoeWarps * 32)
 moe_table_down_kernel(const T* __restrict__ act, const int* __restrict__ ids, const int* __restrict__ table, int vocab,
                       int top, int experts, const T* __restrict__ down, const T* __restrict__ base, int base_stride,
-                      float weight, T* __restrict__ out, int width, int ff) {
+                      float weight, const float* __restrict__ weights, T* __restrict__ out, int width, int ff) {
     extern __shared__ float as[];                       // [top][ff]
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int i = threadIdx.x; i < top * ff; i += blockDim.x) as[i] = to_f32(act[(size_t)t * top * ff + i]);
     __syncthreads();
-    const int id = ids[t];
+    const int id = ids ? ids[t] : t;
     const bool id_ok = id >= 0 && id < vocab;
     const int i0 = blockIdx.y * kMoeOutsPerBlock;
     for (int i = i0 + warp; i < min(width, i0 + kMoeOutsPerBlock); i += kMoeWarps) {
@@ -107,10 +125,11 @@ moe_table_down_kernel(const T* __restrict__ act, const int* __restrict__ ids, co
         for (int k = 0; k < top; ++k) {
             const int e = id_ok ? table[(size_t)id * top + k] : -1;
             if (e < 0 || e >= experts) continue;
-            sum += dot_row(down + ((size_t)e * width + i) * ff, as + k * ff, ff, lane);
+            const float dot = dot_row(down + ((size_t)e * width + i) * ff, as + k * ff, ff, lane);
+            sum += weights ? weights[(size_t)t * top + k] * dot : dot;
         }
         if (lane == 0) {
-            float v = sum * weight;
+            float v = weights ? sum : sum * weight;
             if (base) v += to_f32(base[(size_t)t * base_stride + i]);
             out[(size_t)t * width + i] = from_f32<T>(v);
         }
@@ -123,16 +142,16 @@ using namespace cib;
 
 extern "C" int cib_moe_table_gate_up(const void* h, int h_stride, int dtype, const int* ids, const int* table, int vocab,
                                      int top, int experts, const void* gate_up, void* act, int num_tokens, int width,
-                                     int ff, cudaStream_t stream) {
+                                     int ff, int act_kind, float limit, cudaStream_t stream) {
     CIB_REQUIRE(num_tokens >= 0 && top > 0 && experts > 0 && width > 0 && ff > 0 && vocab > 0, "moe_table: bad sizes");
     CIB_REQUIRE(width <= 12 * 1024, "moe_table: width %d too large for this kernel", width);
     if (num_tokens == 0) return 0;
     dim3 grid(num_tokens * top, (ff + kMoeOutsPerBlock - 1) / kMoeOutsPerBlock);
     const size_t smem = (size_t)width * sizeof(float);
     if (dtype == kF32)
-        moe_table_gate_up_kernel<float><<<grid, kMoeWarps * 32, smem, stream>>>((const float*)h, h_stride, ids, table, vocab, top, experts, (const float*)gate_up, (float*)act, width, ff);
+        moe_table_gate_up_kernel<float><<<grid, kMoeWarps * 32, smem, stream>>>((const float*)h, h_stride, ids, table, vocab, top, experts, (const float*)gate_up, (float*)act, width, ff, ExpertAct{act_kind, limit});
     else if (dtype == kBF16)
-        moe_table_gate_up_kernel<__nv_bfloat16><<<grid, kMoeWarps * 32, smem, stream>>>((const __nv_bfloat16*)h, h_stride, ids, table, vocab, top, experts, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)act, width, ff);
+        moe_table_gate_up_kernel<__nv_bfloat16><<<grid, kMoeWarps * 32, smem, stream>>>((const __nv_bfloat16*)h, h_stride, ids, table, vocab, top, experts, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)act, width, ff, ExpertAct{act_kind, limit});
     else
         CIB_REQUIRE(false, "moe_table: unsupported dtype %d", dtype);
     CIB_LAUNCH_CHECK("moe_table_gate_up");
@@ -141,16 +160,16 @@ extern "C" int cib_moe_table_gate_up(const void* h, int h_stride, int dtype, con
 
 extern "C" int cib_moe_table_down(const void* act, int dtype, const int* ids, const int* table, int vocab, int top,
                                   int experts, const void* down, const void* base, int base_stride, float weight,
-                                  void* out, int num_tokens, int width, int ff, cudaStream_t stream) {
+                                  const float* weights, void* out, int num_tokens, int width, int ff, cudaStream_t stream) {
     CIB_REQUIRE(num_tokens >= 0 && top > 0 && experts > 0 && width > 0 && ff > 0 && vocab > 0, "moe_table: bad sizes");
     CIB_REQUIRE((size_t)top * ff <= 12 * 1024, "moe_table: %d x %d activations too large for this kernel", top, ff);
     if (num_tokens == 0) return 0;
     dim3 grid(num_tokens, (width + kMoeOutsPerBlock - 1) / kMoeOutsPerBlock);
     const size_t smem = (size_t)top * ff * sizeof(float);
     if (dtype == kF32)
-        moe_table_down_kernel<float><<<grid, kMoeWarps * 32, smem, stream>>>((const float*)act, ids, table, vocab, top, experts, (const float*)down, (const float*)base, base_stride, weight, (float*)out, width, ff);
+        moe_table_down_kernel<float><<<grid, kMoeWarps * 32, smem, stream>>>((const float*)act, ids, table, vocab, top, experts, (const float*)down, (const float*)base, base_stride, weight, weights, (float*)out, width, ff);
     else if (dtype == kBF16)
-        moe_table_down_kernel<__nv_bfloat16><<<grid, kMoeWarps * 32, smem, stream>>>((const __nv_bfloat16*)act, ids, table, vocab, top, experts, (const __nv_bfloat16*)down, (const __nv_bfloat16*)base, base_stride, weight, (__nv_bfloat16*)out, width, ff);
+        moe_table_down_kernel<__nv_bfloat16><<<grid, kMoeWarps * 32, smem, stream>>>((const __nv_bfloat16*)act, ids, table, vocab, top, experts, (const __nv_bfloat16*)down, (const __nv_bfloat16*)base, base_stride, weight, weights, (__nv_bfloat16*)out, width, ff);
     else
         CIB_REQUIRE(false, "moe_table: unsupported dtype %d", dtype);
     CIB_LAUNCH_CHECK("moe_table_down");
@@ -183,7 +202,7 @@ moe_route_kernel(const int* __restrict__ ids, const int* __restrict__ table, int
     for (int e = threadIdx.x; e < experts; e += blockDim.x) { counts[e] = 0; cursor[e] = 0; }
     __syncthreads();
     auto expert_of = [&](int slot) {
-        const int id = ids[slot / top];
+        const int id = ids ? ids[slot / top] : slot / top;
         const int e = (id >= 0 && id < vocab) ? table[(size_t)id * top + slot % top] : -1;
         return (e >= 0 && e < experts) ? e : -1;
     };
@@ -227,7 +246,7 @@ __global__ void __launch_bounds__(128)
 moe_grouped_gemm_kernel(const __nv_bfloat16* __restrict__ a, int lda, const int* __restrict__ gather, int top,
                         const __nv_bfloat16* __restrict__ w, long long w_expert, __nv_bfloat16* __restrict__ out, int ldo,
                         const int* __restrict__ offsets, const int* __restrict__ tile_expert,
-                        const int* __restrict__ tile_row0, const int* __restrict__ num_tiles, int N, int K) {
+                        const int* __restrict__ tile_row0, const int* __restrict__ num_tiles, int N, int K, ExpertAct fn) {
     __shared__ __align__(16) __nv_bfloat16 sA[kGStages][kGM][kGLd];
     __shared__ __align__(16) __nv_bfloat16 sB[kGStages][2][kGN][kGLd];
     if ((int)blockIdx.x >= *num_tiles) return;
@@ -319,8 +338,8 @@ moe_grouped_gemm_kernel(const __nv_bfloat16* __restrict__ a, int lda, const int*
             for (int nt = 0; nt < kGN / 8; ++nt) {
                 const int col = n0 + nt * 8 + quad * 2;
                 const float g0 = acc[0][nt][2 * hrow], g1 = acc[0][nt][2 * hrow + 1];
-                const float v0 = g0 / (1.f + expf(-g0)) * acc[1][nt][2 * hrow];
-                const float v1 = g1 / (1.f + expf(-g1)) * acc[1][nt][2 * hrow + 1];
+                const float v0 = fn(g0, acc[1][nt][2 * hrow]);
+                const float v1 = fn(g1, acc[1][nt][2 * hrow + 1]);
                 if (col + 1 < N) *reinterpret_cast<uint32_t*>(dst + col) = pack_bf16(v0, v1);
                 else if (col < N) dst[col] = __float2bfloat16_rn(v0);
             }
@@ -339,15 +358,15 @@ moe_grouped_gemm_kernel(const __nv_bfloat16* __restrict__ a, int lda, const int*
 
 __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ slot_pos, int top,
                                    const __nv_bfloat16* __restrict__ base, int base_stride, float weight,
-                                   __nv_bfloat16* __restrict__ out, int width) {
+                                   const float* __restrict__ weights, __nv_bfloat16* __restrict__ out, int width) {
     const int t = blockIdx.x;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
         float sum = 0.f;
         for (int k = 0; k < top; ++k) {
             const int at = slot_pos[t * top + k];
-            if (at >= 0) sum += __bfloat162float(y[(size_t)at * width + i]);
+            if (at >= 0) sum += (weights ? weights[t * top + k] : 1.f) * __bfloat162float(y[(size_t)at * width + i]);
         }
-        float v = sum * weight;
+        float v = weights ? sum : sum * weight;
         if (base) v += __bfloat162float(base[(size_t)t * base_stride + i]);
         out[(size_t)t * width + i] = __float2bfloat16_rn(v);
     }
@@ -369,8 +388,8 @@ extern "C" long long cib_moe_table_grouped_workspace_ints(int num_tokens, int to
 // bfloat16 only.  act: [T * top, ff] and y: [T * top, width] scratch rows; ints: see above.
 extern "C" int cib_moe_table_grouped(const void* h, int h_stride, const int* ids, const int* table, int vocab, int top,
                                      int experts, const void* gate_up, const void* down, const void* base, int base_stride,
-                                     float weight, void* out, void* act, void* y, int* ints, int num_tokens, int width,
-                                     int ff, cudaStream_t stream) {
+                                     float weight, const float* weights, void* out, void* act, void* y, int* ints,
+                                     int num_tokens, int width, int ff, int act_kind, float limit, cudaStream_t stream) {
     using namespace cib;
     CIB_REQUIRE(num_tokens >= 0 && top > 0 && vocab > 0, "moe_table_grouped: bad sizes");
     CIB_REQUIRE(cib_moe_table_grouped_supports(width, ff, experts), "moe_table_grouped: width %d / ff %d / %d experts are not taken", width, ff, experts);
@@ -393,15 +412,15 @@ extern "C" int cib_moe_table_grouped(const void* h, int h_stride, const int* ids
     dim3 g1(max_tiles, (ff + kGN - 1) / kGN);
     moe_grouped_gemm_kernel<true><<<g1, 128, 0, stream>>>((const __nv_bfloat16*)h, h_stride, sorted_slot, top,
                                                           (const __nv_bfloat16*)gate_up, (long long)2 * ff * width,
-                                                          (__nv_bfloat16*)act, ff, offsets, tile_expert, tile_row0, num_tiles, ff, width);
+                                                          (__nv_bfloat16*)act, ff, offsets, tile_expert, tile_row0, num_tiles, ff, width, ExpertAct{act_kind, limit});
     CIB_LAUNCH_CHECK("moe_grouped_gate_up");
     dim3 g2(max_tiles, (width + 2 * kGN - 1) / (2 * kGN));
     moe_grouped_gemm_kernel<false><<<g2, 128, 0, stream>>>((const __nv_bfloat16*)act, ff, nullptr, top, (const __nv_bfloat16*)down,
                                                            (long long)width * ff, (__nv_bfloat16*)y, width, offsets, tile_expert,
-                                                           tile_row0, num_tiles, width, ff);
+                                                           tile_row0, num_tiles, width, ff, ExpertAct{0, 0.f});
     CIB_LAUNCH_CHECK("moe_grouped_down");
     moe_combine_kernel<<<num_tokens, 256, 0, stream>>>((const __nv_bfloat16*)y, slot_pos, top, (const __nv_bfloat16*)base, base_stride,
-                                                       weight, (__nv_bfloat16*)out, width);
+                                                       weight, weights, (__nv_bfloat16*)out, width);
     CIB_LAUNCH_CHECK("moe_combine");
     return 0;
 }

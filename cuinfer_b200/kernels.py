@@ -78,9 +78,18 @@ def _declare(lib: ctypes.CDLL) -> None:
                                      _F, _I, _P],
         "cib_gemm_generic_batched": [_P, _I, ctypes.c_longlong, _P, _I, ctypes.c_longlong, _I, _P, _I, ctypes.c_longlong, _I,
                                      _I, _I, _I, _I, _P],
-        "cib_moe_table_gate_up": [_P, _I, _I, _P, _P, _I, _I, _I, _P, _P, _I, _I, _I, _P],
-        "cib_moe_table_grouped": [_P, _I, _P, _P, _I, _I, _I, _P, _P, _P, _I, _F, _P, _P, _P, _P, _I, _I, _I, _P],
-        "cib_moe_table_down": [_P, _I, _P, _P, _I, _I, _I, _P, _P, _I, _F, _P, _I, _I, _I, _P],
+        "cib_moe_table_gate_up": [_P, _I, _I, _P, _P, _I, _I, _I, _P, _P, _I, _I, _I, _I, _F, _P],
+        "cib_moe_table_grouped": [_P, _I, _P, _P, _I, _I, _I, _P, _P, _P, _I, _F, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _P],
+        "cib_moe_table_down": [_P, _I, _P, _P, _I, _I, _I, _P, _P, _I, _F, _P, _P, _I, _I, _I, _P],
+        "cib_window_attention_prep": [_P, _I, _I, _P, _P, _P, _I, _F, _I, _I, _I, _I, _P, _I, _P, _I, _P, ctypes.c_longlong, _I, _I, _P],
+        "cib_window_attention_generic": [_P, _I, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _I, _P],
+        "cib_mlstm_scan": [_P, _P, _P, _I, _I, _P, _I, _P, _P, _I, _F, _F, _F, _P, _P, _P, _I, _I, _P, _I, _I, _I, _P],
+        "cib_delta_prep": [_P, _I, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _P, _I, _P],
+        "cib_delta_scan": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _P, _I, _I, _P, _I, _I, _I, _P],
+        "cib_head_rms_gate": [_P, _P, _I, _I, _P, _I, _I, _F, _I, _P, _I, _I, _I, _P],
+        "cib_router_topk": [_P, _I, _I, _I, _P, _P, _I, _P],
+        "cib_rms_stream": [_P, _P, _I, _P, _I, _F, _P, _I, _F, _P, _P, _I, _I, _I, _P],
+        "cib_gelu_tanh": [_P, _P, _I, _P, _I, _P, _I, _I, _I, _P],
         "cib_add_rmsnorm": [_P, _P, _I, _P, _I, _F, _P, _I, _I, _I, _P],
         "cib_gather_rows": [_P, _P, _I, _P, _P, _I, _I, _I, _P],
         "cib_silu_mul": [_P, _P, _I, _I, _I, _P],
@@ -637,9 +646,13 @@ def gemm_generic_batched(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) ->
 MOE_GROUPED_MIN_ROWS = 128
 
 
-def moe_table_feed_forward(h: torch.Tensor, ids: torch.Tensor, table: torch.Tensor, gate_up: torch.Tensor,
-                           down: torch.Tensor, base: torch.Tensor | None, out: torch.Tensor) -> None:
+def moe_table_feed_forward(h: torch.Tensor, ids: torch.Tensor | None, table: torch.Tensor, gate_up: torch.Tensor,
+                           down: torch.Tensor, base: torch.Tensor | None, out: torch.Tensor,
+                           weights: torch.Tensor | None = None, clamp_limit: float | None = None) -> None:
     """out[t] = base[t] + (1/top) * sum over k of expert(table[ids[t], k])(h[t]) with gated experts
+    (``ids`` None: the table has a row per row of ``h`` — experts chosen by a router; ``weights`` float32 [T, top]:
+    a weight per choice instead of 1/top; ``clamp_limit``: the experts' activation is
+    ``g * sigmoid(1.702 g) * (u + 1)`` with ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)``)
     ``down_e(silu(gate_e h) * up_e h)``; ``gate_up[E, 2 ff, W]`` (gate rows first), ``down[E, W, ff]``, ``table[V, top]``.
     Few rows, 32-bit, or sizes that are not multiples of 32: two launches (a matrix-vector product per token and
     choice).  Many bfloat16 rows: grouped by expert (see ``MOE_GROUPED_MIN_ROWS``)."""
@@ -651,6 +664,13 @@ def moe_table_feed_forward(h: torch.Tensor, ids: torch.Tensor, table: torch.Tens
         raise KernelError("moe_table: weights, rows and out do not fit")
     if h.stride(1) != 1 or (base is not None and (base.shape != (T, W) or base.stride(1) != 1 or base.dtype != h.dtype)):
         raise KernelError("moe_table: rows must be dense and of one dtype")
+    if ids is None and V != T:
+        raise KernelError("moe_table: without token ids the table needs a row per row of h")
+    if weights is not None and weights.shape != (T, top):
+        raise KernelError("moe_table: weights must be [rows, top]")
+    p_ids = _cuda(ids, "ids", torch.int32) if ids is not None else None
+    p_w = _cuda(weights, "weights", torch.float32) if weights is not None else None
+    act_kind, limit = (1, float(clamp_limit)) if clamp_limit is not None else (0, 0.0)
     lib = library()
     if (h.dtype == torch.bfloat16 and T * top >= MOE_GROUPED_MIN_ROWS and h.stride(0) % 8 == 0
             and lib.cib_moe_table_grouped_supports(W, ff, E)):
@@ -659,22 +679,22 @@ def moe_table_feed_forward(h: torch.Tensor, ids: torch.Tensor, table: torch.Tens
         y = torch.empty((T * top, W), dtype=h.dtype, device=h.device)
         ints = torch.empty(lib.cib_moe_table_grouped_workspace_ints(T, top, E), dtype=torch.int32, device=h.device)
         rc = lib.cib_moe_table_grouped(
-            _cuda(h, "h", contiguous=False), h.stride(0), _cuda(ids, "ids", torch.int32), _cuda(table, "table", torch.int32), V, top, E,
+            _cuda(h, "h", contiguous=False), h.stride(0), p_ids, _cuda(table, "table", torch.int32), V, top, E,
             _cuda(gate_up, "gate_up"), _cuda(down, "down"), _cuda(base, "base", contiguous=False) if base is not None else None,
-            base.stride(0) if base is not None else 0, 1.0 / top, _cuda(out, "out"), _cuda(act, "act"), _cuda(y, "y"),
-            _cuda(ints, "ints"), T, W, ff, _stream())
+            base.stride(0) if base is not None else 0, 1.0 / top, p_w, _cuda(out, "out"), _cuda(act, "act"), _cuda(y, "y"),
+            _cuda(ints, "ints"), T, W, ff, act_kind, limit, _stream())
         _check(rc, "moe_table_grouped")
         for _ in range(4):
             _count()
         return
     act = torch.empty((T, top, ff), dtype=h.dtype, device=h.device)
-    rc = lib.cib_moe_table_gate_up(_cuda(h, "h", contiguous=False), h.stride(0), _code(h, "h"), _cuda(ids, "ids", torch.int32),
+    rc = lib.cib_moe_table_gate_up(_cuda(h, "h", contiguous=False), h.stride(0), _code(h, "h"), p_ids,
                                    _cuda(table, "table", torch.int32), V, top, E, _cuda(gate_up, "gate_up"), _cuda(act, "act"),
-                                   T, W, ff, _stream())
+                                   T, W, ff, act_kind, limit, _stream())
     _check(rc, "moe_table_gate_up")
-    rc = lib.cib_moe_table_down(_cuda(act, "act"), _code(act, "act"), _cuda(ids, "ids", torch.int32), _cuda(table, "table", torch.int32),
+    rc = lib.cib_moe_table_down(_cuda(act, "act"), _code(act, "act"), p_ids, _cuda(table, "table", torch.int32),
                                 V, top, E, _cuda(down, "down"), _cuda(base, "base", contiguous=False) if base is not None else None,
-                                base.stride(0) if base is not None else 0, 1.0 / top, _cuda(out, "out"), T, W, ff, _stream())
+                                base.stride(0) if base is not None else 0, 1.0 / top, p_w, _cuda(out, "out"), T, W, ff, _stream())
     _check(rc, "moe_table_down")
     _count()
     _count()
@@ -919,4 +939,196 @@ def sample(logits: torch.Tensor, params: torch.Tensor, out_ids: torch.Tensor) ->
     rc = library().cib_sample(_cuda(logits, "logits", torch.float32, contiguous=False), logits.stride(0), S, V,
                               _cuda(params, "params"), _cuda(out_ids, "out_ids", torch.int32), _stream())
     _check(rc, "sample")
+    _count()
+
+
+# ---- RMS norms around the residual sum, GELU ---------------------------------------------------------------------------
+
+def rms_stream(residual: torch.Tensor, delta: torch.Tensor | None, post: tuple | None, pre: tuple | None,
+               out: torch.Tensor | None, raw: torch.Tensor | None = None) -> None:
+    """One pass over the 32-bit residual rows: ``residual += rmsnorm(delta) * post_gain`` (``post = (gain, eps)``; a plain
+    ``+= delta`` when ``post`` is None), ``raw = residual`` rounded to its dtype, ``out = rmsnorm(residual) * gain``
+    with ``pre = (gain, eps)``.  Every part may be left out."""
+    rows, H = residual.shape
+    for name, t in (("delta", delta), ("out", out), ("raw", raw)):
+        if t is not None and t.shape != residual.shape:
+            raise KernelError(f"rms_stream: {name} {list(t.shape)} does not match residual {list(residual.shape)}")
+    if out is not None and raw is not None and out.dtype != raw.dtype:
+        raise KernelError("rms_stream: out and raw must have one dtype")
+    if (post is not None and post[0].numel() != H) or (pre is not None and pre[0].numel() != H):
+        raise KernelError(f"rms_stream: gains must have {H} elements")
+    if out is not None and pre is None:
+        raise KernelError("rms_stream: out needs the norm's gain")
+    target = out if out is not None else raw
+    rc = library().cib_rms_stream(
+        _cuda(residual, "residual", torch.float32), _cuda(delta, "delta") if delta is not None else None,
+        _code(delta, "delta") if delta is not None else 0,
+        _cuda(post[0], "post gain") if post else None, _code(post[0], "post gain") if post else 0, float(post[1]) if post else 0.0,
+        _cuda(pre[0], "gain") if pre else None, _code(pre[0], "gain") if pre else 0, float(pre[1]) if pre else 0.0,
+        _cuda(out, "out") if out is not None else None, _cuda(raw, "raw") if raw is not None else None,
+        _code(target, "out") if target is not None else 0, rows, H, _stream())
+    _check(rc, "rms_stream")
+    _count()
+
+
+def gelu_tanh(x: torch.Tensor, out: torch.Tensor, table: torch.Tensor | None = None, ids: torch.Tensor | None = None) -> None:
+    """out = gelu_tanh(x) element by element; with ``table`` [V, cols] (rows may be a column range of wider rows) and
+    ``ids`` [rows], each row is also multiplied by ``table[ids[row]]``."""
+    rows, cols = x.shape
+    if out.shape != x.shape or out.dtype != x.dtype or not x.is_contiguous():
+        raise KernelError("gelu_tanh: out does not fit x")
+    if table is not None and (ids is None or table.shape[1] != cols or table.dtype != x.dtype or table.stride(1) != 1):
+        raise KernelError("gelu_tanh: the table does not fit x")
+    rc = library().cib_gelu_tanh(
+        _cuda(x, "x"), _cuda(table, "table", contiguous=False) if table is not None else None,
+        table.stride(0) if table is not None else 0, _cuda(ids, "ids", torch.int32) if table is not None else None,
+        table.shape[0] if table is not None else 0, _cuda(out, "out"), _code(x, "x"), rows, cols, _stream())
+    _check(rc, "gelu_tanh")
+    _count()
+
+
+def router_topk(logits: torch.Tensor, top: int, choice: torch.Tensor, weight: torch.Tensor) -> None:
+    """From float32 logits [T, E]: ``choice`` int32 [T, top] (largest logits first, the lower index wins a tie) and
+    ``weight`` float32 [T, top], the softmax over the chosen logits."""
+    T, E = logits.shape
+    if choice.shape != (T, top) or weight.shape != (T, top) or logits.stride(1) != 1:
+        raise KernelError("router_topk: shapes do not fit")
+    rc = library().cib_router_topk(_cuda(logits, "logits", torch.float32, contiguous=False), logits.stride(0), E, top,
+                                   _cuda(choice, "choice", torch.int32), _cuda(weight, "weight", torch.float32), T, _stream())
+    _check(rc, "router_topk")
+    _count()
+
+
+# ---- attention with a capped score and a window that keeps the first tokens ---------------------------------------------------
+
+def window_attention_prep(qkv: torch.Tensor, positions: torch.Tensor, slot_mapping: torch.Tensor | None,
+                          freq: torch.Tensor | None, rot_dims: int, eps: float, num_heads: int, num_kv_heads: int, dim: int,
+                          vdim: int, v_first: torch.Tensor | None, mix: torch.Tensor | None, cache: torch.Tensor | None) -> None:
+    """On the packed rows ``[q | k | v]``: rotary encoding (neighbouring pairs, the first ``rot_dims`` values, 32-bit
+    angle ``pos * freq[i]``) and unit RMS of every query and key head; queries are rewritten in place; keys and values
+    (``(1 - mix) * v + mix * v_first`` when both are given) go to ``cache[page, 0, kv head, slot, dim + vdim]``."""
+    T, stride = qkv.shape
+    if stride < (num_heads + num_kv_heads) * dim + num_kv_heads * vdim or qkv.stride(1) != 1:
+        raise KernelError("window_attention_prep: rows are too short")
+    if cache is not None:
+        if cache.dim() != 5 or cache.shape[1] != 1 or cache.shape[2] != num_kv_heads or cache.shape[4] != dim + vdim or cache.dtype != qkv.dtype:
+            raise KernelError(f"window_attention_prep: cache must be [pages, 1, {num_kv_heads}, page, {dim + vdim}] of the rows' dtype")
+        if slot_mapping is None:
+            raise KernelError("window_attention_prep: a cache write needs slot_mapping")
+    if (v_first is None) != (mix is None):
+        raise KernelError("window_attention_prep: mixing needs both the values and the factor")
+    if v_first is not None and (v_first.shape != (T, num_kv_heads * vdim) or v_first.dtype != qkv.dtype or v_first.stride(1) != 1):
+        raise KernelError("window_attention_prep: v_first does not fit")
+    rc = library().cib_window_attention_prep(
+        _cuda(qkv, "qkv", contiguous=False), _code(qkv, "qkv"), qkv.stride(0), _cuda(positions, "positions", torch.int32),
+        _cuda(slot_mapping, "slot_mapping", torch.int32) if cache is not None else None,
+        _cuda(freq, "freq", torch.float32) if freq is not None and rot_dims else None, rot_dims if freq is not None else 0,
+        float(eps), num_heads, num_kv_heads, dim, vdim,
+        _cuda(v_first, "v_first", contiguous=False) if v_first is not None else None, v_first.stride(0) if v_first is not None else 0,
+        _cuda(mix, "mix") if mix is not None else None, _code(mix, "mix") if mix is not None else 0,
+        _cuda(cache, "cache") if cache is not None else None, cache.shape[0] * cache.shape[3] if cache is not None else 0,
+        cache.shape[3] if cache is not None else 1, T, _stream())
+    _check(rc, "window_attention_prep")
+    _count()
+
+
+def window_attention_generic(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
+                             positions: torch.Tensor, token_request: torch.Tensor, num_heads: int, num_kv_heads: int,
+                             dim: int, vdim: int, scale: float, softcap: float, window: int, keep_first: int) -> None:
+    """Attention of the query rows ``q[:, :H * dim]`` over the paged cache of [key | value] rows; ``out`` [T, H * vdim].
+    ``softcap`` 0: no cap; ``window`` 0: every earlier key."""
+    T = q.shape[0]
+    if q.stride(1) != 1 or out.shape != (T, num_heads * vdim) or out.dtype != q.dtype or cache.dtype != q.dtype or not out.is_contiguous():
+        raise KernelError("window_attention: out/cache do not fit q")
+    rc = library().cib_window_attention_generic(
+        _cuda(q, "q", contiguous=False), _code(q, "q"), q.stride(0), _cuda(out, "out"), out.stride(0), _cuda(cache, "cache"),
+        cache.shape[0], cache.shape[3], _cuda(block_table, "block_table", torch.int32, contiguous=False), block_table.stride(0),
+        _cuda(positions, "positions", torch.int32), _cuda(token_request, "token_request", torch.int32), T, num_heads,
+        num_kv_heads, dim, vdim, float(scale), float(softcap or 0.0), int(window or 0), int(keep_first or 0), _stream())
+    _check(rc, "window_attention_generic")
+    _count()
+
+
+# ---- mixers with a matrix state ------------------------------------------------------------------------------------------------
+
+def mlstm_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gates: torch.Tensor, i_bias: torch.Tensor,
+               f_bias: torch.Tensor, cap: float, q_scale: float, state: torch.Tensor, query_start_loc: torch.Tensor,
+               state_slots: torch.Tensor, out: torch.Tensor, num_heads: int, dim: int, vdim: int, floor: float = 1e-6) -> None:
+    """The matrix memory with exponential gates over every request's rows, from and to its state slot.  ``q``, ``k``, ``v``
+    are column ranges of the same packed rows; ``gates`` float32 [T, 2H] (input then forget pre-activations);
+    ``state`` float32 [slots, H, dim * vdim + dim + 1]; ``out`` float32 [T, H * vdim]."""
+    T = out.shape[0]
+    R = state_slots.numel()
+    if not (q.stride(0) == k.stride(0) == v.stride(0)) or not (q.dtype == k.dtype == v.dtype) or q.stride(1) != 1:
+        raise KernelError("mlstm_scan: q, k and v must be column ranges of the same rows")
+    if state.shape[1:] != (num_heads, dim * vdim + dim + 1) or gates.shape != (T, 2 * num_heads) or out.shape != (T, num_heads * vdim):
+        raise KernelError("mlstm_scan: state, gates or out do not fit")
+    if i_bias.dtype != f_bias.dtype:
+        raise KernelError("mlstm_scan: the biases must have one dtype")
+    rc = library().cib_mlstm_scan(
+        _cuda(q, "q", contiguous=False), _cuda(k, "k", contiguous=False), _cuda(v, "v", contiguous=False), _code(q, "q"), q.stride(0),
+        _cuda(gates, "gates", torch.float32), gates.stride(0), _cuda(i_bias, "i_bias"), _cuda(f_bias, "f_bias"), _code(i_bias, "i_bias"),
+        float(cap), float(q_scale), float(floor), _cuda(state, "state", torch.float32),
+        _cuda(query_start_loc, "query_start_loc", torch.int32), _cuda(state_slots, "state_slots", torch.int32), state.shape[0], R,
+        _cuda(out, "out", torch.float32), num_heads, dim, vdim, _stream())
+    _check(rc, "mlstm_scan")
+    _count()
+
+
+def delta_prep(x: torch.Tensor, taps: torch.Tensor, conv_state: torch.Tensor, query_start_loc: torch.Tensor,
+               token_request: torch.Tensor, state_slots: torch.Tensor, num_kv_heads: int, num_heads: int, dim: int, vdim: int,
+               unit_eps: float, q_scale: float, out: torch.Tensor) -> None:
+    """Short causal convolution + SiLU over the channels ``[q | k | v]`` of the packed rows ``x`` (continuing from, and
+    updating, each request's ``conv_state`` float32 [slots, taps - 1, C]), then unit q and k heads, q times ``q_scale``;
+    ``out`` float32 [T, C].  Two launches."""
+    T = x.shape[0]
+    C = 2 * num_kv_heads * dim + num_heads * vdim
+    K = taps.shape[1]
+    if taps.shape != (C, K) or taps.dtype != x.dtype or out.shape != (T, C) or x.stride(1) != 1 or x.shape[1] < C:
+        raise KernelError("delta_prep: taps, rows or out do not fit")
+    if conv_state.shape[1:] != (max(K - 1, 1), C):
+        raise KernelError("delta_prep: conv_state must be [slots, taps - 1, channels]")
+    rc = library().cib_delta_prep(
+        _cuda(x, "x", contiguous=False), _code(x, "x"), x.stride(0), _cuda(taps, "taps"), K, _cuda(conv_state, "conv_state", torch.float32),
+        _cuda(query_start_loc, "query_start_loc", torch.int32), _cuda(token_request, "token_request", torch.int32),
+        _cuda(state_slots, "state_slots", torch.int32), conv_state.shape[0], state_slots.numel(), num_kv_heads, num_heads, dim, vdim,
+        float(unit_eps), float(q_scale), _cuda(out, "out", torch.float32), T, _stream())
+    _check(rc, "delta_prep")
+    _count()
+    _count()
+
+
+def delta_scan(qkv: torch.Tensor, gates: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor,
+               query_start_loc: torch.Tensor, state_slots: torch.Tensor, out: torch.Tensor, num_kv_heads: int, num_heads: int,
+               dim: int, vdim: int) -> None:
+    """The gated delta rule over every request's rows.  ``qkv`` float32 [T, C] from ``delta_prep``; ``gates`` float32
+    [T, 2H] (beta then decay pre-activations); ``state`` float32 [slots, H, dim * vdim]; ``out`` float32 [T, H * vdim]."""
+    T = qkv.shape[0]
+    if state.shape[1:] != (num_heads, dim * vdim) or gates.shape != (T, 2 * num_heads) or out.shape != (T, num_heads * vdim):
+        raise KernelError("delta_scan: state, gates or out do not fit")
+    if a_log.dtype != dt_bias.dtype:
+        raise KernelError("delta_scan: the per-head vectors must have one dtype")
+    rc = library().cib_delta_scan(
+        _cuda(qkv, "qkv", torch.float32), num_kv_heads, _cuda(gates, "gates", torch.float32), gates.stride(0), _cuda(a_log, "a_log"),
+        _cuda(dt_bias, "dt_bias"), _code(a_log, "a_log"), _cuda(state, "state", torch.float32),
+        _cuda(query_start_loc, "query_start_loc", torch.int32), _cuda(state_slots, "state_slots", torch.int32), state.shape[0],
+        state_slots.numel(), _cuda(out, "out", torch.float32), num_heads, dim, vdim, _stream())
+    _check(rc, "delta_scan")
+    _count()
+
+
+def head_rms_gate(o: torch.Tensor, gate: torch.Tensor, gain: torch.Tensor, eps: float, silu: bool, out: torch.Tensor,
+                  num_heads: int, vdim: int) -> None:
+    """out[t, h, :] = rmsnorm(o[t, h, :]) * gain * act(gate[t, h, :]); ``gain`` has ``vdim`` elements (shared by the heads)
+    or ``H * vdim``; act is SiLU or the sigmoid; ``o`` float32, ``gate`` a column range of the packed rows."""
+    T = o.shape[0]
+    if o.shape != (T, num_heads * vdim) or out.shape != o.shape or gate.shape != o.shape or gate.stride(1) != 1 or gate.dtype != out.dtype:
+        raise KernelError("head_rms_gate: shapes do not fit")
+    if gain.numel() not in (vdim, num_heads * vdim):
+        raise KernelError("head_rms_gate: the gain must have vdim or heads * vdim elements")
+    rc = library().cib_head_rms_gate(
+        _cuda(o, "o", torch.float32), _cuda(gate, "gate", contiguous=False), _code(gate, "gate"), gate.stride(0), _cuda(gain, "gain"),
+        _code(gain, "gain"), 1 if gain.numel() != vdim else 0, float(eps), 1 if silu else 0,
+        _cuda(out, "out"), num_heads, vdim, T, _stream())
+    _check(rc, "head_rms_gate")
     _count()

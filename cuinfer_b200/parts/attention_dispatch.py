@@ -73,3 +73,10 @@ def latent_attention(q_abs: torch.Tensor, q: torch.Tensor, out: torch.Tensor, kv
         return
     kernels.latent_attention_generic(q_abs, q, out, kv.cache, kv.group.block_table, ctx.query_start_loc, ctx.seq_lens,
                                      ctx.token_request, ctx.positions, freq, rot_dims, sinks, num_heads, dn, rk, dr, scale, window)
+
+
+def window_attention(q: torch.Tensor, out: torch.Tensor, kv: PagedKV, ctx: StepContext, num_heads: int, num_kv_heads: int,
+                     dim: int, vdim: int, scale: float, softcap: float, window: int, keep_first: int) -> None:
+    """Attention over cached [key | value] rows with a capped score and a window that keeps the first tokens."""
+    kernels.window_attention_generic(q, out, kv.cache, kv.group.block_table, ctx.positions, ctx.token_request, num_heads,
+                                     num_kv_heads, dim, vdim, scale, softcap, window, keep_first)

@@ -4,7 +4,10 @@
 (csrc/model/causal_lm.cpp:138-188).  Each sub-layer's output stays pending until the next norm, which
 adds it to the 32-bit residual and normalises in one pass (the reference fuses only the first add,
 csrc/ops/residual_rms_norm_fused.cu:58-109); the last pending delta of the last layer is folded by
-the model's final norm.  Spec: ``PartSpec("prenorm", norm_names=(first, second))``.
+the model's final norm.  Spec: ``PartSpec("prenorm", norm_names=(first, second), after=None)``.  A layer whose
+feed-forward is of kind ``none`` has the mixer's sub-layer only.  ``after``: the spec of a part from the ``TAILS``
+registry that runs on the stream once both sub-layers are done (a per-layer input from the token's id, say), with
+``index`` set to the layer's place among the model's layers.
 """
 from __future__ import annotations
 
@@ -12,7 +15,7 @@ from typing import Callable, List
 
 from .base import Block, FeedForward, LazyNorm, Mixer, Norm, Part, ResidualStream
 from .context import StepContext
-from .registry import BLOCKS
+from .registry import BLOCKS, TAILS
 from .spec import PartSpec
 
 
@@ -23,16 +26,30 @@ class PreNormBlock(Block):
         super().__init__(spec, mixer=mixer, feed_forward=feed_forward, make_norm=make_norm, prefix=prefix)
         first, second = spec.get("norm_names", ("input_layernorm", "post_attention_layernorm"))
         self.mixer_norm = make_norm(f"{prefix}.{first}")
-        self.feed_forward_norm = make_norm(f"{prefix}.{second}")
+        self.has_feed_forward = not getattr(feed_forward, "absent", False)
+        self.feed_forward_norm = make_norm(f"{prefix}.{second}") if self.has_feed_forward else None
+        after = spec.get("after")
+        self.tail = None
+        if after is not None:
+            self.tail = TAILS.get(after.kind)(after, hidden_size=mixer.hidden_size, prefix=f"{prefix}.{after.get('name', 'side')}",
+                                              dtype=mixer.dtype)
 
     def parts(self) -> List[Part]:
-        return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
+        out: List[Part] = [self.mixer_norm, self.mixer]
+        if self.has_feed_forward:
+            out += [self.feed_forward_norm, self.feed_forward]
+        if self.tail is not None:
+            out += self.tail.parts()
+        return out
 
     def forward(self, stream: ResidualStream, ctx: StepContext, run: int) -> None:
         h = self._normed(stream, self.mixer_norm, self.mixer)
         stream.pending = self.mixer.forward(h, ctx, run)
-        h = self._normed(stream, self.feed_forward_norm, self.feed_forward)
-        stream.pending = self.feed_forward.forward(h, ctx)
+        if self.has_feed_forward:
+            h = self._normed(stream, self.feed_forward_norm, self.feed_forward)
+            stream.pending = self.feed_forward.forward(h, ctx)
+        if self.tail is not None:
+            self.tail.forward(stream, ctx)
 
     @staticmethod
     def _normed(stream: ResidualStream, norm: Norm, consumer: Part):

@@ -60,6 +60,9 @@ class StepContext:
     kv: Dict[int, PagedKV] = field(default_factory=dict)          # run index -> its paged cache
     state: Dict[int, torch.Tensor] = field(default_factory=dict)  # run index -> [slots, *state shape]
     decode_only: bool = False        # every request brings exactly one token
+    # What one layer run leaves for later runs of the SAME step (rows of this step's tokens, by a key the parts agree
+    # on): a layer's values that later layers mix into their own, for instance.  Nothing here outlives the step.
+    shared: Dict[str, torch.Tensor] = field(default_factory=dict)
 
     def query_lens_for_launch(self) -> List[int]:
         """Tokens per request as host integers, for sizing a launch (how many row tiles an attention kernel needs).

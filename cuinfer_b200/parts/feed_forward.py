@@ -98,6 +98,18 @@ class SquaredReluFeedForward(FeedForward):
         return self.down.forward(act)
 
 
+@FEED_FORWARDS.register("gelu_tanh")
+class GeluFeedForward(SquaredReluFeedForward):
+    """``down( gelu_tanh(up(x)) )`` with the tanh form of GELU, no gate, no biases.  Spec: ``PartSpec("gelu_tanh",
+    intermediate_size=I, names=(up, down))``."""
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        y = self.up.forward(x)
+        act = torch.empty_like(y)
+        kernels.gelu_tanh(y, act)
+        return self.down.forward(act)
+
+
 @FEED_FORWARDS.register("moe_table")
 class TableRoutedExperts(FeedForward):
     """A mixture of SiLU-gated experts without a router: an integer table ``[vocab, top]`` names, for every token id,
@@ -165,4 +177,63 @@ class TableRoutedExperts(FeedForward):
             base = self.shared_down.forward(self.shared_gate_up.forward(x, silu_pair=True))
         out = torch.empty((x.shape[0], self.hidden_size), dtype=x.dtype, device=x.device)
         kernels.moe_table_feed_forward(x, ctx.token_ids, self.table, self.gate_up, self.down, base, out)
+        return out
+
+
+@FEED_FORWARDS.register("moe_routed")
+class RoutedExperts(FeedForward):
+    """A mixture of gated experts chosen by a router: logits ``z = R h`` in 32 bits, the ``top`` largest win, their
+    weights are the softmax over the chosen logits only, and the output is the weighted sum of the chosen experts.
+    An expert is ``down(act(gate h, up h))``, no biases; ``activation="clamped"`` with ``limit`` L is
+    ``g = min(gate h, L), u = clamp(up h, -L, L), act = g * sigmoid(1.702 g) * (u + 1)``; ``activation="silu"`` is
+    ``silu(gate h) * up h``.
+
+    Spec: ``PartSpec("moe_routed", experts=E, top=k, intermediate_size=I, activation, limit, router_name="router",
+    expert_names=("e{}.gate", "e{}.up", "e{}.down"))``.  The experts' matrices are stacked at load as for the table-routed
+    mixture, whose kernels run the experts here too (rows by token and choice for few rows, grouped by expert on the
+    tensor cores for many)."""
+
+    def __init__(self, spec: PartSpec, *, hidden_size: int, prefix: str, dtype: torch.dtype) -> None:
+        super().__init__(spec, hidden_size=hidden_size, prefix=prefix, dtype=dtype)
+        self.experts, self.top, self.intermediate_size = int(spec.experts), int(spec.top), int(spec.intermediate_size)
+        if not 0 < self.top <= self.experts:
+            raise ValueError(f"moe_routed: top={self.top} of {self.experts} experts")
+        self.activation = spec.get("activation", "silu")
+        if self.activation not in ("silu", "clamped"):
+            raise ValueError(f"moe_routed: activation {self.activation!r} is not silu or clamped")
+        self.limit = float(spec.limit) if self.activation == "clamped" else None
+        gate, up, down = spec.get("expert_names", ("e{}.gate", "e{}.up", "e{}.down"))
+        p = prefix
+        self._gate_up_specs = [TensorSpec(f"{p}.{n.format(e)}", (self.intermediate_size, hidden_size))
+                               for e in range(self.experts) for n in (gate, up)]
+        self._down_specs = [TensorSpec(f"{p}.{down.format(e)}", (hidden_size, self.intermediate_size)) for e in range(self.experts)]
+        self.router = Linear([f"{p}.{spec.get('router_name', 'router')}"], [self.experts], hidden_size, dtype)
+        self.gate_up: Optional[torch.Tensor] = None
+        self.down: Optional[torch.Tensor] = None
+
+    def tensors(self) -> List[TensorSpec]:
+        return self._gate_up_specs + self._down_specs + self.router.tensors()
+
+    def load(self, store) -> None:
+        E, I, H = self.experts, self.intermediate_size, self.hidden_size
+        self.gate_up = store.get_stacked(self._gate_up_specs).to(self.dtype).view(E, 2 * I, H)
+        self.down = store.get_stacked(self._down_specs).to(self.dtype).view(E, H, I)
+        self.router.load(store)
+
+    def first_weight(self) -> Optional[torch.Tensor]:
+        return self.router.weight
+
+    def workspace_bytes(self, tokens: int) -> int:
+        width = 2 if self.dtype == torch.bfloat16 else 4
+        return (tokens * (self.top * (self.intermediate_size + self.hidden_size) + self.hidden_size) * width
+                + tokens * (self.top * 24 + self.experts * 4))
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        T = x.shape[0]
+        logits = self.router.forward(x, out_dtype=torch.float32)
+        choice = torch.empty((T, self.top), dtype=torch.int32, device=x.device)
+        weight = torch.empty((T, self.top), dtype=torch.float32, device=x.device)
+        kernels.router_topk(logits, self.top, choice, weight)
+        out = torch.empty((T, self.hidden_size), dtype=x.dtype, device=x.device)
+        kernels.moe_table_feed_forward(x, None, choice, self.gate_up, self.down, None, out, weights=weight, clamp_limit=self.limit)
         return out

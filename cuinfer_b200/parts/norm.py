@@ -1,6 +1,10 @@
 """RMSNorm: ``out = x · rsqrt(mean(x²) + eps) · w`` with the squares, the mean, the rsqrt and the product
 in 32 bits and one rounding at the end (csrc/ops/rms_norm.cu:43-71; eps inside the square root, the
-weight multiplies directly).  Spec: ``PartSpec("rmsnorm", eps=...)``.
+weight multiplies directly).  Spec: ``PartSpec("rmsnorm", eps=..., weight_suffix=".weight")``: the gain is the tensor
+``prefix + weight_suffix``.
+
+The RMS norm also serves on a sub-layer's OUTPUT (a delta that is normed before it joins the residual): as
+``stream.pending_norm`` it is folded by the next RMS norm of the stream in the same kernel, or alone by ``fold``.
 """
 from __future__ import annotations
 
@@ -22,7 +26,8 @@ class RMSNorm(Norm):
         self.weight: torch.Tensor | None = None
 
     def tensors(self) -> List[TensorSpec]:
-        return [TensorSpec(f"{self.prefix}.weight", (self.hidden_size,), keep_stored_precision=True, init="ones")]
+        return [TensorSpec(self.prefix + self.spec.get("weight_suffix", ".weight"), (self.hidden_size,),
+                           keep_stored_precision=True, init="ones")]
 
     def load(self, store) -> None:
         self.weight = store.get(self.tensors()[0])
@@ -31,11 +36,21 @@ class RMSNorm(Norm):
         return (self.weight, self.eps) if self.weight is not None else None
 
     def add_norm(self, stream: ResidualStream) -> torch.Tensor:
-        stream.settle()
         out = torch.empty(stream.residual.shape, dtype=self.dtype, device=stream.residual.device)
+        post = stream.pending_norm
+        if isinstance(post, RMSNorm) and stream.extra is None and stream.pending is not None:
+            # the delta goes through its own RMS norm, joins the residual and the sum is normed: one kernel
+            kernels.rms_stream(stream.residual, stream.pending, (post.weight, post.eps), (self.weight, self.eps), out)
+            stream.pending = stream.pending_norm = None
+            return out
+        stream.settle()
         kernels.add_rmsnorm(stream.residual, stream.pending, self.weight, self.eps, out)
         stream.pending = None
         return out
+
+    def fold(self, stream: ResidualStream) -> None:
+        kernels.rms_stream(stream.residual, stream.pending, (self.weight, self.eps), None, None)
+        stream.pending = stream.pending_norm = None
 
     def norm_rows(self, rows: torch.Tensor) -> torch.Tensor:
         out = torch.empty(rows.shape, dtype=self.dtype, device=rows.device)

@@ -8,6 +8,7 @@ handed to the kernel that applies it.  ``none``: no encoding.
 """
 from __future__ import annotations
 
+import math
 from typing import Optional
 
 import torch
@@ -68,7 +69,10 @@ class RotaryInterleaved(PositionEncoding):
     element 2i pairs with 2i+1 and the pair (u, v) at position p becomes ``(u cos a - v sin a, v cos a + u sin a)`` with
     ``a = p * f_i``, ``f_i = theta ** (-2i / rotary_dim)``.  There is no table and hence no largest position: the
     kernels that apply it take the frequencies (32-bit, rounded once from double precision) and compute the angle and
-    its full-range sine and cosine in 32 bits.  Spec: ``PartSpec("rope_interleaved", theta=..., rotary_dim=...)``."""
+    its full-range sine and cosine in 32 bits.  Spec: ``PartSpec("rope_interleaved", theta=..., rotary_dim=...,
+    scaling=None)``.  ``scaling = (factor, low, high, original)`` rescales the frequencies by wavelength
+    ``l = 2 pi / f`` against a context of ``original`` tokens: kept where ``l < original / high``, divided by ``factor``
+    where ``l > original / low``, and in between ``(1 - s) f / factor + s f`` with ``s = (original / l - low) / (high - low)``."""
 
     def __init__(self, spec: PartSpec, *, hidden_size: int, prefix: str, dtype: torch.dtype) -> None:
         super().__init__(spec, hidden_size=hidden_size, prefix=prefix, dtype=dtype)
@@ -76,12 +80,24 @@ class RotaryInterleaved(PositionEncoding):
         self.rotary_dim = int(spec.rotary_dim)
         if self.rotary_dim < 0 or self.rotary_dim % 2 or not self.theta > 0:
             raise ValueError(f"rope_interleaved: rotary_dim must be even and theta positive, got {self.rotary_dim}, {self.theta}")
+        scaling = spec.get("scaling")
+        self.scaling = tuple(float(v) for v in scaling) if scaling else None
+        if self.scaling is not None and (len(self.scaling) != 4 or self.scaling[0] <= 0 or self.scaling[2] == self.scaling[1]
+                                         or self.scaling[1] <= 0 or self.scaling[2] <= 0 or self.scaling[3] <= 0):
+            raise ValueError(f"rope_interleaved: scaling must be (factor, low, high, original) with low != high, got {scaling}")
         self._freq: Optional[torch.Tensor] = None
         self._device: Optional[torch.device] = None
 
     def host_frequencies(self) -> torch.Tensor:
         i = torch.arange(self.rotary_dim // 2, dtype=torch.float64)
-        return torch.pow(torch.tensor(self.theta, dtype=torch.float64), -2.0 * i / max(self.rotary_dim, 1)).float()
+        f = torch.pow(torch.tensor(self.theta, dtype=torch.float64), -2.0 * i / max(self.rotary_dim, 1))
+        if self.scaling is not None:
+            factor, low, high, original = self.scaling
+            wavelength = 2.0 * math.pi / f
+            s = (original / wavelength - low) / (high - low)
+            blended = (1.0 - s) * f / factor + s * f
+            f = torch.where(wavelength < original / high, f, torch.where(wavelength > original / low, f / factor, blended))
+        return f.float()
 
     def load(self, store) -> None:
         self._device = store.device
@@ -92,7 +108,7 @@ class RotaryInterleaved(PositionEncoding):
             return None
         if self._freq is None:
             device = torch.device(self._device or "cuda")
-            key = ("interleaved", self.theta, self.rotary_dim, str(device))
+            key = ("interleaved", self.theta, self.rotary_dim, self.scaling, str(device))
             if key not in _TABLES:
                 _TABLES[key] = self.host_frequencies().to(device)
             self._freq = _TABLES[key]

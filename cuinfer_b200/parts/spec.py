@@ -140,19 +140,24 @@ class PagedCacheNeed:
 
     ``window``: None keeps every token; ``w`` keeps only the last ``w`` (pages that a request's
     next query can no longer see are given back).  ``planes``: how many rows of ``head_dim`` a head keeps per
-    token — 2 for keys and values, 1 for a mixer that derives both from one cached row (a latent).
+    token — 2 for keys and values, 1 for a mixer that derives both from one cached row (a latent) or that keeps a
+    token's key and value side by side in one row.  ``keep_first``: with a window, the first so many tokens of a request
+    stay visible (and their pages held) however far the window has moved.
     """
 
     num_kv_heads: int
     head_dim: int
     window: int | None = None
     planes: int = 2
+    keep_first: int = 0
 
 
 @dataclass(frozen=True)
 class StateNeed:
     """What a mixer keeps per request, whatever its length: one tensor of ``shape``/``dtype``
-    per run, zeroed when a request is admitted."""
+    per run, zeroed when a request is admitted.  A mixer that keeps several tensors returns a tuple of these, each with
+    a ``name``; ``StepContext.run_state(run)`` is then a dict from name to ``[slots, *shape]``."""
 
     shape: tuple[int, ...]
     dtype: str = "float32"
+    name: str = ""
