@@ -173,9 +173,11 @@ def expert_ff(h, gate, up, down, limit):
     return (g * torch.sigmoid(1.702 * g) * (u + 1.0)) @ down.T
 
 
-def moe_ff(h, w, f: dict):
+def moe_ff(h, w, f: dict, routers=None):
     E, top, limit = int(f["router"]["experts"]), int(f["router"]["top"]), float(f["expert"]["limit"])
     z = h @ w["router"].T
+    if routers is not None:
+        routers.append((top, z))
     vals, idx = torch.topk(z, top, dim=-1)
     p = torch.softmax(vals, -1)
     out = torch.zeros_like(h)
@@ -198,8 +200,9 @@ def _sub(weights: Dict[str, torch.Tensor], prefix: str) -> Dict[str, torch.Tenso
     return {k[len(prefix):]: v for k, v in weights.items() if k.startswith(prefix)}
 
 
-def forward(config: dict, weights: Dict[str, torch.Tensor], tokens, tap=None):
-    """Logits [T, vocab] of one sequence; ``tap(i, x)`` sees the stream after every layer."""
+def forward(config: dict, weights: Dict[str, torch.Tensor], tokens, tap=None, routers=None):
+    """Logits [T, vocab] of one sequence; ``tap(i, x)`` sees the stream after every layer; ``routers``, a list, collects
+    ``(top, logits)`` of every routed feed-forward."""
     eps = float(config["norm"]["eps"])
     tokens = torch.as_tensor(tokens, dtype=torch.long)
     x = weights["embed"][tokens]
@@ -228,9 +231,112 @@ def forward(config: dict, weights: Dict[str, torch.Tensor], tokens, tap=None):
         if f:
             h = rms_norm(x, weights[p + "norm2"], eps)
             fw = _sub(weights, p + "mlp.")
-            x = x + (dense_ff(h, fw) if f["kind"] == "dense" else moe_ff(h, fw, f))
+            x = x + (dense_ff(h, fw) if f["kind"] == "dense" else moe_ff(h, fw, f, routers))
         if side:
             x = token_side(x, tokens, i, int(side["dim"]), _sub(weights, p + "side."), weights["side.embed"], eps)
         if tap is not None:
             tap(i, x)
     return rms_norm(x, weights["final.norm"], eps) @ weights["head"].T
+
+
+def greedy(config: dict, weights: Dict[str, torch.Tensor], prompt, steps: int) -> List[int]:
+    """Greedy continuation, recomputing the whole sequence every step (the lower id wins a tie)."""
+    toks = list(prompt)
+    out = []
+    for _ in range(steps):
+        nxt = int(torch.argmax(forward(config, weights, toks)[-1]))
+        out.append(nxt)
+        toks.append(nxt)
+    return out
+
+
+# ---- random weights for the tests -------------------------------------------------------------------------------------------------
+def random_model(config: dict, seed: int, dtype=torch.float32) -> Dict[str, torch.Tensor]:
+    """Weights whose values are bfloat16 numbers.  The routers are made robust against rounding, so that a bfloat16
+    engine and this implementation choose the same experts: the first E columns of the embedding carry, per token id, a
+    ranking of the experts in steps of 1.5; every tensor that writes into the stream is small in those columns; a router's
+    row e reads column e (plus a little of everything else, so that the weights still depend on the context)."""
+    g = torch.Generator().manual_seed(seed)
+    W, V = config["width"], config["vocab"]
+    E_max = max([L["mlp"]["router"]["experts"] for L in config["layers"] if L.get("mlp") and L["mlp"]["kind"] == "moe"] + [0])
+
+    def mat(o, i, gain=1.0):
+        return (torch.randn(o, i, generator=g) * gain / math.sqrt(i)).bfloat16().to(dtype)
+
+    def vec(n, around=0.0, spread=0.1):
+        return (around + spread * torch.randn(n, generator=g)).bfloat16().to(dtype)
+
+    def writer(i, gain=1.0):                         # [W, i]: output rows of the router's columns are small
+        m = torch.randn(W, i, generator=g) * gain / math.sqrt(i)
+        m[:E_max] *= 0.05
+        return m.bfloat16().to(dtype)
+
+    embed = torch.randn(V, W, generator=g)
+    for tok in range(V):
+        ranks = torch.randperm(E_max, generator=g) if E_max else []
+        for e in range(E_max):
+            embed[tok, e] = 7.5 - 1.5 * float(ranks[e])
+    t: Dict[str, torch.Tensor] = {"embed": embed.bfloat16().to(dtype), "head": mat(V, W, 2.0), "final.norm": vec(W, 1.0)}
+    side = config.get("token_side")
+    if side:
+        t["side.embed"] = (torch.randn(V, len(config["layers"]) * side["dim"], generator=g)).bfloat16().to(dtype)
+    for i, L in enumerate(config["layers"]):
+        p = f"l{i}."
+        m = L["mixer"]
+        t[p + "norm1"] = vec(W, 1.0)
+        if L["type"] == "attention":
+            H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            t[p + "mix.q"], t[p + "mix.k"], t[p + "mix.v"] = mat(H * d, W), mat(G * d, W), mat(G * dv, W)
+            t[p + "mix.o"] = writer(H * dv)
+            if m.get("v_mix"):
+                t[p + "mix.vmix"] = (0.2 + 0.5 * torch.rand((), generator=g)).bfloat16().to(dtype)
+        elif L["type"] == "mlstm":
+            H, d, dv = m["heads"], m["dim"], m["vdim"]
+            t[p + "mix.q"], t[p + "mix.k"], t[p + "mix.v"], t[p + "mix.g"] = mat(H * d, W, 2.0), mat(H * d, W, 2.0), mat(H * dv, W), mat(H * dv, W)
+            t[p + "mix.i"], t[p + "mix.f"] = mat(H, W, 3.0), mat(H, W, 3.0)
+            t[p + "mix.i.b"], t[p + "mix.f.b"] = vec(H, 0.0, 1.0), vec(H, 2.0, 1.0)
+            t[p + "mix.norm"] = vec(H * dv, 1.0)
+            t[p + "mix.o"] = writer(H * dv)
+        else:
+            H, G, d, dv, K = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["conv"]
+            t[p + "mix.q"], t[p + "mix.k"], t[p + "mix.v"], t[p + "mix.g"] = mat(G * d, W, 2.0), mat(G * d, W, 2.0), mat(H * dv, W, 2.0), mat(H * dv, W)
+            for n, size in (("q", G * d), ("k", G * d), ("v", H * dv)):
+                t[p + f"mix.{n}.conv"] = (torch.randn(size, K, generator=g) * 0.6).bfloat16().to(dtype)
+            t[p + "mix.b"], t[p + "mix.a"] = mat(H, W, 2.0), mat(H, W, 2.0)
+            t[p + "mix.A_log"], t[p + "mix.dt_bias"] = vec(H, -1.0, 0.7), vec(H, 0.0, 1.0)
+            t[p + "mix.norm"] = vec(dv, 1.0)
+            t[p + "mix.o"] = writer(H * dv)
+        f = L.get("mlp")
+        if f:
+            t[p + "norm2"] = vec(W, 1.0)
+            if f["kind"] == "dense":
+                t[p + "mlp.up"], t[p + "mlp.down"] = mat(f["ff"], W), writer(f["ff"])
+            else:
+                E, ff = f["router"]["experts"], f["expert"]["ff"]
+                for e in range(E):
+                    t[f"{p}mlp.e{e}.gate"], t[f"{p}mlp.e{e}.up"], t[f"{p}mlp.e{e}.down"] = mat(ff, W, 2.0), mat(ff, W, 2.0), writer(ff)
+                router = torch.randn(E, W, generator=g) * 0.05 / math.sqrt(W)
+                router[:, :E_max] = 0.0
+                for e in range(E):
+                    router[e, e] = 2.0
+                t[p + "mlp.router"] = router.bfloat16().to(dtype)
+                t[p + "norm2"][:E_max] = 1.0
+        if side:
+            t[p + "side.gate"], t[p + "side.proj"] = mat(side["dim"], W), mat(W, side["dim"])
+            gain = 0.5 + 0.1 * torch.randn(W, generator=g)
+            gain[:E_max] = 0.02
+            t[p + "side.norm"] = gain.bfloat16().to(dtype)
+    return t
+
+
+def router_margin(config: dict, weights: Dict[str, torch.Tensor], tokens) -> float:
+    """The smallest gap between the last chosen and the first rejected router logit over the sequence's tokens and
+    layers, as a fraction of the spread of the logits (tests assert that their weights leave a safe margin)."""
+    logits: List[torch.Tensor] = []
+    forward(config, weights, tokens, routers=logits)
+    worst = math.inf
+    for top, z in logits:
+        if top < z.shape[1]:
+            s = torch.sort(z, dim=-1, descending=True).values
+            worst = min(worst, float(((s[:, top - 1] - s[:, top]) / (s[:, 0] - s[:, -1]).clamp_min(1e-9)).min()))
+    return worst
