@@ -1,0 +1,316 @@
+// Attention with a capped score and a window that keeps the first tokens, on the tensor cores (bfloat16), for steps
+// that bring prompt portions (alone or beside decoded tokens).  Same arithmetic as the all-sizes kernel in
+// attention_window.cu; same tiling as this package's paged prefill kernel (attention_prefill.cu): the rows of a tile are
+// (query token x query head of one kv head) folded together, 64 rows a CTA (16 a warp), 64-key tiles copied row by row
+// with cp.async into two swizzled shared-memory stages, ldmatrix + mma.sync m16n8k16 with 32-bit accumulation, running
+// softmax in base 2 with the scores in registers.  What differs:
+//   * keys (DK values) and values (DV values) have sizes of their own and lie side by side in a cache row
+//     [page][kv head][slot][DK + DV];
+//   * score = scale * q.k, then cap * tanh(score / cap) when cap > 0 (32-bit; tanh through the exponential);
+//   * a query at position i sees key j when j <= i and (window == 0 or i - j < window or j < keep_first): a tile walks
+//     the key tiles of the kept tokens that lie before its window (keys 0 .. min(keep_first, window start) - 1) and then
+//     those from its window's start to its last query.
+// The softmax weights are rounded to bfloat16 for the second product; everything before that is 32-bit.
+#include "mma_utils.cuh"
+
+namespace cib {
+
+constexpr int kWmWarps = 4;
+constexpr int kWmM = 64;     // rows per CTA
+constexpr int kWmN = 64;     // keys per tile
+constexpr int kWmStages = 2;
+
+// where chunk `c` (8 values) of row `r` lies in a shared-memory row of CH chunks: conflict-free for ldmatrix
+template <int CH>
+__device__ __forceinline__ int wm_swz(int r, int c) {
+    if (CH >= 8) return c ^ (r & 7);
+    return c ^ ((r >> 1) & (CH - 1));
+}
+
+template <int DK, int DV>
+__device__ __forceinline__ void wm_load_kv_tile(__nv_bfloat16* sK, __nv_bfloat16* sV, const __nv_bfloat16* cache,
+                                                const int* table, int key0, int key_end, int page_size, int num_pages,
+                                                int nkv, int kvh, int tid) {
+    constexpr int kCK = DK / 8, kCV = DV / 8, kC = kCK + kCV;
+    for (int idx = tid; idx < kWmN * kC; idx += kWmWarps * 32) {
+        const int row = idx / kC, chunk = idx % kC;
+        const int j = key0 + row;
+        bool valid = j < key_end;
+        int page = 0, off = 0;
+        if (valid) {
+            page = table[j / page_size];
+            off = j % page_size;
+            valid = page >= 0 && page < num_pages;
+        }
+        const __nv_bfloat16* src = cache + (((size_t)(valid ? page : 0) * nkv + kvh) * page_size + (valid ? off : 0)) * (DK + DV) + chunk * 8;
+        __nv_bfloat16* dst = chunk < kCK ? sK + row * DK + wm_swz<kCK>(row, chunk) * 8
+                                         : sV + row * DV + wm_swz<kCV>(row, chunk - kCK) * 8;
+        cp_async16(dst, src, valid);
+    }
+}
+
+template <int DK, int DV>
+__global__ void __launch_bounds__(kWmWarps * 32, 2)
+window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* __restrict__ out,
+                            int out_stride, const __nv_bfloat16* __restrict__ cache, int num_pages, int page_size,
+                            const int* __restrict__ block_table, int table_stride,
+                            const int* __restrict__ query_start_loc, const int* __restrict__ seq_lens,
+                            int num_requests, int nq, int nkv, float scale, float cap, int window, int keep_first) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __shared__ int s_req, s_tile;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int quad = lane & 3, qrow = lane >> 2;
+    const int kvh = blockIdx.y;
+    const int g = nq / nkv;
+    constexpr int kCK = DK / 8, kCV = DV / 8;
+    constexpr float kLog2e = 1.4426950408889634f;
+
+    if (tid == 0) {
+        int t = blockIdx.x, r = 0;
+        for (; r < num_requests; ++r) {
+            const int tiles = ((query_start_loc[r + 1] - query_start_loc[r]) * g + kWmM - 1) / kWmM;
+            if (t < tiles) break;
+            t -= tiles;
+        }
+        s_req = r;
+        s_tile = t;
+    }
+    __syncthreads();
+    const int r = s_req;
+    if (r >= num_requests) return;
+    const int q0 = query_start_loc[r];
+    const int n = query_start_loc[r + 1] - q0;
+    const int seq_len = seq_lens[r];
+    const int rows_total = n * g;
+    const int row0 = s_tile * kWmM;
+    const int* table = block_table + (size_t)r * table_stride;
+
+    constexpr int kStageElems = kWmN * (DK + DV);
+    __nv_bfloat16* sKV = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+    __nv_bfloat16* sQ = sKV + (size_t)kStageElems;            // the query tile borrows stage 1 (DK <= DK + DV)
+    auto stage_k = [&](int s) { return sKV + (size_t)s * kStageElems; };
+    auto stage_v = [&](int s) { return sKV + (size_t)s * kStageElems + kWmN * DK; };
+
+    // ---- key tiles: the kept tokens before the window, then the window up to the last query ----
+    const int last_row = min(row0 + kWmM, rows_total) - 1;
+    const int pos_first = seq_len - n + row0 / g;
+    const int pos_last = seq_len - n + last_row / g;
+    int k_lo = window > 0 ? max(0, pos_first - window + 1) : 0;
+    k_lo = k_lo / kWmN * kWmN;
+    const int k_hi = pos_last + 1;
+    const int kept_end = window > 0 ? min(keep_first, k_lo) : 0;
+    const int kept_tiles = (kept_end + kWmN - 1) / kWmN;
+    const int num_tiles = kept_tiles + (k_hi - k_lo + kWmN - 1) / kWmN;
+    auto tile_key0 = [&](int t) { return t < kept_tiles ? t * kWmN : k_lo + (t - kept_tiles) * kWmN; };
+    auto tile_end = [&](int t) { return t < kept_tiles ? kept_end : k_hi; };
+
+    {
+        for (int idx = tid; idx < kWmM * kCK; idx += kWmWarps * 32) {
+            const int row = idx / kCK, chunk = idx % kCK;
+            const int grow = row0 + row;
+            const bool valid = grow < rows_total;
+            const int tl = valid ? grow / g : 0, hi = valid ? grow % g : 0;
+            const __nv_bfloat16* src = q + (size_t)(q0 + tl) * q_stride + (size_t)(kvh * g + hi) * DK + chunk * 8;
+            cp_async16(sQ + row * DK + wm_swz<kCK>(row, chunk) * 8, src, valid);
+        }
+        cp_async_commit();
+    }
+    wm_load_kv_tile<DK, DV>(stage_k(0), stage_v(0), cache, table, tile_key0(0), tile_end(0), page_size, num_pages, nkv, kvh, tid);
+    cp_async_commit();
+
+    cp_async_wait<1>();
+    __syncthreads();
+    uint32_t qf[DK / 16][4];
+    {
+        const int mat = lane >> 3, rr = lane & 7;
+        const int row = warp * 16 + (mat & 1) * 8 + rr;
+#pragma unroll
+        for (int kt = 0; kt < DK / 16; ++kt) {
+            const int chunk = 2 * kt + (mat >> 1);
+            ldmatrix_x4(qf[kt], smem_u32(sQ + row * DK + wm_swz<kCK>(row, chunk) * 8));
+        }
+    }
+    __syncthreads();          // every warp has its query fragments: stage 1 may now take keys and values
+    int pos_row[2];
+    bool row_ok[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int grow = row0 + warp * 16 + qrow + 8 * h;
+        row_ok[h] = grow < rows_total;
+        pos_row[h] = row_ok[h] ? seq_len - n + grow / g : -1;
+    }
+
+    float o[DV / 8][4];
+#pragma unroll
+    for (int i = 0; i < DV / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    float m_run[2] = {-INFINITY, -INFINITY};
+    float l_run[2] = {0.f, 0.f};
+    const float inv_cap = cap > 0.f ? 1.f / cap : 0.f;
+
+    for (int t = 0; t < num_tiles; ++t) {
+        const int key0 = tile_key0(t);
+        const bool kept_tile = t < kept_tiles;
+        if (t + 1 < num_tiles)
+            wm_load_kv_tile<DK, DV>(stage_k((t + 1) % kWmStages), stage_v((t + 1) % kWmStages), cache, table, tile_key0(t + 1),
+                                    tile_end(t + 1), page_size, num_pages, nkv, kvh, tid);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        const __nv_bfloat16* sK = stage_k(t % kWmStages);
+        const __nv_bfloat16* sV = stage_v(t % kWmStages);
+
+        float s[kWmN / 8][4];
+#pragma unroll
+        for (int nt = 0; nt < kWmN / 8; ++nt) { s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f; }
+        {
+            const int mat = lane >> 3, rr = lane & 7;
+#pragma unroll
+            for (int kt = 0; kt < DK / 16; ++kt) {
+#pragma unroll
+                for (int np = 0; np < kWmN / 16; ++np) {
+                    const int krow = np * 16 + (mat >> 1) * 8 + rr;
+                    const int chunk = 2 * kt + (mat & 1);
+                    uint32_t b[4];
+                    ldmatrix_x4(b, smem_u32(sK + krow * DK + wm_swz<kCK>(krow, chunk) * 8));
+                    mma_bf16_16816(s[2 * np], qf[kt], b[0], b[1]);
+                    mma_bf16_16816(s[2 * np + 1], qf[kt], b[2], b[3]);
+                }
+            }
+        }
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nt = 0; nt < kWmN / 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int h = e >> 1;
+                float v = s[nt][e] * scale;
+                if (cap > 0.f) {
+                    // cap * tanh(v / cap) = cap * (1 - 2 / (exp(2 v / cap) + 1)); the exponent is bounded so that it stays finite
+                    const float x = fminf(fmaxf(2.f * v * inv_cap, -60.f), 60.f);
+                    v = cap * (1.f - 2.f / (__expf(x) + 1.f));
+                }
+                v *= kLog2e;
+                const int key = key0 + nt * 8 + quad * 2 + (e & 1);
+                const int pos = pos_row[h];
+                const bool vis = kept_tile ? (key < kept_end && pos >= 0)
+                                           : (key <= pos && (window <= 0 || key > pos - window || key < keep_first));
+                v = vis ? v : -INFINITY;
+                s[nt][e] = v;
+                mx[h] = fmaxf(mx[h], v);
+            }
+        }
+        float corr[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+            const float m_new = fmaxf(m_run[h], mx[h]);
+            corr[h] = m_run[h] == -INFINITY ? 0.f : exp2f(m_run[h] - m_new);
+            m_run[h] = m_new;
+            l_run[h] *= corr[h];
+        }
+#pragma unroll
+        for (int nt = 0; nt < kWmN / 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float mref = m_run[e >> 1];
+                const float p = (s[nt][e] == -INFINITY || mref == -INFINITY) ? 0.f : exp2f(s[nt][e] - mref);
+                s[nt][e] = p;
+                l_run[e >> 1] += p;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < DV / 8; ++i) { o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1]; }
+        {
+            const int mat = lane >> 3, rr = lane & 7;
+#pragma unroll
+            for (int kp = 0; kp < kWmN / 16; ++kp) {
+                uint32_t pf[4];
+                pf[0] = pack_bf16(s[2 * kp][0], s[2 * kp][1]);
+                pf[1] = pack_bf16(s[2 * kp][2], s[2 * kp][3]);
+                pf[2] = pack_bf16(s[2 * kp + 1][0], s[2 * kp + 1][1]);
+                pf[3] = pack_bf16(s[2 * kp + 1][2], s[2 * kp + 1][3]);
+                const int vrow = kp * 16 + (mat & 1) * 8 + rr;
+#pragma unroll
+                for (int nt = 0; nt < DV / 16; ++nt) {
+                    const int chunk = 2 * nt + (mat >> 1);
+                    uint32_t b[4];
+                    ldmatrix_x4_trans(b, smem_u32(sV + vrow * DV + wm_swz<kCV>(vrow, chunk) * 8));
+                    mma_bf16_16816(o[2 * nt], pf, b[0], b[1]);
+                    mma_bf16_16816(o[2 * nt + 1], pf, b[2], b[3]);
+                }
+            }
+        }
+        __syncthreads();      // every warp is done with this stage before it is filled again
+    }
+    cp_async_wait<0>();
+
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        float l = l_run[h];
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        if (!row_ok[h]) continue;
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        const int grow = row0 + warp * 16 + qrow + 8 * h;
+        const int tl = grow / g, hi = grow % g;
+        __nv_bfloat16* dst = out + (size_t)(q0 + tl) * out_stride + (size_t)(kvh * g + hi) * DV;
+#pragma unroll
+        for (int nt = 0; nt < DV / 8; ++nt) {
+            *reinterpret_cast<uint32_t*>(dst + nt * 8 + quad * 2) = pack_bf16(o[nt][2 * h] * inv, o[nt][2 * h + 1] * inv);
+        }
+    }
+}
+
+template <int DK, int DV>
+static int launch_window_mma(const void* q, int q_stride, void* out, int out_stride, const void* cache, int num_pages,
+                             int page_size, const int* block_table, int table_stride, const int* query_start_loc,
+                             const int* seq_lens, int num_requests, int num_tiles, int nq, int nkv, float scale, float cap,
+                             int window, int keep_first, cudaStream_t stream) {
+    const size_t smem = (size_t)(kWmStages * kWmN * (DK + DV)) * sizeof(__nv_bfloat16);
+    static SmemLimit limit;
+    if (int rc = raise_smem_limit(limit, window_attention_mma_kernel<DK, DV>, smem, "window_attention_mma")) return rc;
+    dim3 grid(num_tiles, nkv);
+    window_attention_mma_kernel<DK, DV><<<grid, kWmWarps * 32, smem, stream>>>(
+        (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)cache, num_pages,
+        page_size, block_table, table_stride, query_start_loc, seq_lens, num_requests, nq, nkv, scale, cap, window, keep_first);
+    CIB_LAUNCH_CHECK("window_attention_mma");
+    return 0;
+}
+
+}  // namespace cib
+
+using namespace cib;
+
+extern "C" int cib_window_attention_mma_supports(int dim, int vdim, int nq, int nkv) {
+    return (dim == 64 || dim == 128) && (vdim == 32 || vdim == 64 || vdim == 128) && nkv > 0 && nq % nkv == 0;
+}
+
+// num_tiles: the sum over requests of ceil(tokens_r * (nq / nkv) / 64), or any upper bound of it (CTAs that find no
+// tile leave).
+extern "C" int cib_window_attention_mma(const void* q, int q_stride, void* out, int out_stride, const void* cache,
+                                        int num_pages, int page_size, const int* block_table, int table_stride,
+                                        const int* query_start_loc, const int* seq_lens, int num_requests, int num_tiles,
+                                        int nq, int nkv, int dim, int vdim, float scale, float cap, int window,
+                                        int keep_first, cudaStream_t stream) {
+    CIB_REQUIRE(cib_window_attention_mma_supports(dim, vdim, nq, nkv), "window_attention_mma: sizes %d / %d are not taken by this kernel", dim, vdim);
+    CIB_REQUIRE(num_requests >= 0 && num_tiles >= 0 && nkv <= 65535, "window_attention_mma: bad sizes");
+    CIB_REQUIRE(page_size > 0 && num_pages > 0 && table_stride > 0 && window >= 0 && keep_first >= 0, "window_attention_mma: bad cache geometry");
+    CIB_REQUIRE(q_stride % 8 == 0 && ((uintptr_t)q % 16) == 0 && out_stride % 2 == 0 && ((uintptr_t)out % 4) == 0 && ((uintptr_t)cache % 16) == 0,
+                "window_attention_mma: q and cache rows must be 16-byte aligned and out rows 4-byte aligned");
+    if (num_requests == 0 || num_tiles == 0) return 0;
+#define CIB_WM(DKv, DVv)                                                                                                     \
+    if (dim == DKv && vdim == DVv)                                                                                           \
+        return launch_window_mma<DKv, DVv>(q, q_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, \
+                                           query_start_loc, seq_lens, num_requests, num_tiles, nq, nkv, scale, cap, window,     \
+                                           keep_first, stream)
+    CIB_WM(64, 32);
+    CIB_WM(64, 64);
+    CIB_WM(64, 128);
+    CIB_WM(128, 32);
+    CIB_WM(128, 64);
+    CIB_WM(128, 128);
+#undef CIB_WM
+    CIB_REQUIRE(false, "window_attention_mma: no kernel for %d / %d", dim, vdim);
+    return -1;
+}

@@ -83,6 +83,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "cib_moe_table_down": [_P, _I, _P, _P, _I, _I, _I, _P, _P, _I, _F, _P, _P, _I, _I, _I, _P],
         "cib_window_attention_prep": [_P, _I, _I, _P, _P, _P, _I, _F, _I, _I, _I, _I, _P, _I, _P, _I, _P, ctypes.c_longlong, _I, _I, _P],
         "cib_window_attention_generic": [_P, _I, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _I, _P],
+        "cib_window_attention_mma": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I, _P],
         "cib_mlstm_scan": [_P, _P, _P, _I, _I, _P, _I, _P, _P, _I, _F, _F, _F, _P, _P, _P, _I, _I, _P, _I, _I, _I, _P],
         "cib_delta_prep": [_P, _I, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _P, _I, _P],
         "cib_delta_scan": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _P, _I, _I, _P, _I, _I, _I, _P],
@@ -115,6 +116,8 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.cib_moe_table_grouped_supports.restype = _I
     lib.cib_moe_table_grouped_workspace_ints.argtypes = [_I, _I, _I]
     lib.cib_moe_table_grouped_workspace_ints.restype = ctypes.c_longlong
+    lib.cib_window_attention_mma_supports.argtypes = [_I, _I, _I, _I]
+    lib.cib_window_attention_mma_supports.restype = _I
     lib.cib_latent_attention_mma_supports.argtypes = [_I, _I, _I]
     lib.cib_latent_attention_mma_supports.restype = _I
     lib.cib_latent_attention_mma_tiles.argtypes = [_P, _I, _I, _I]
@@ -1046,6 +1049,30 @@ def window_attention_generic(q: torch.Tensor, out: torch.Tensor, cache: torch.Te
         _cuda(positions, "positions", torch.int32), _cuda(token_request, "token_request", torch.int32), T, num_heads,
         num_kv_heads, dim, vdim, float(scale), float(softcap or 0.0), int(window or 0), int(keep_first or 0), _stream())
     _check(rc, "window_attention_generic")
+    _count()
+
+
+def window_attention_mma_supports(dim: int, vdim: int, num_heads: int, num_kv_heads: int) -> bool:
+    return bool(library().cib_window_attention_mma_supports(dim, vdim, num_heads, num_kv_heads))
+
+
+def window_attention_mma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
+                         query_start_loc: torch.Tensor, seq_lens: torch.Tensor, query_lens, num_heads: int, num_kv_heads: int,
+                         dim: int, vdim: int, scale: float, softcap: float, window: int, keep_first: int) -> None:
+    """The same attention on the tensor cores (bfloat16; key sizes 64 or 128, value sizes 32, 64 or 128).  ``query_lens``:
+    tokens per request as host integers, or an upper bound that holds for every batch a captured step replays; they size
+    the launch only."""
+    T = q.shape[0]
+    if q.dtype != torch.bfloat16 or q.stride(1) != 1 or out.shape != (T, num_heads * vdim) or out.dtype != q.dtype or cache.dtype != q.dtype:
+        raise KernelError("window_attention_mma: bfloat16 rows, out [T, H * vdim]")
+    g = num_heads // num_kv_heads
+    tiles = sum((n * g + 63) // 64 for n in query_lens)
+    rc = library().cib_window_attention_mma(
+        _cuda(q, "q", contiguous=False), q.stride(0), _cuda(out, "out"), out.stride(0), _cuda(cache, "cache"), cache.shape[0],
+        cache.shape[3], _cuda(block_table, "block_table", torch.int32, contiguous=False), block_table.stride(0),
+        _cuda(query_start_loc, "query_start_loc", torch.int32), _cuda(seq_lens, "seq_lens", torch.int32), seq_lens.numel(), tiles,
+        num_heads, num_kv_heads, dim, vdim, float(scale), float(softcap or 0.0), int(window or 0), int(keep_first or 0), _stream())
+    _check(rc, "window_attention_mma")
     _count()
 
 

@@ -129,7 +129,8 @@ def _check(folders, name, dtype, steps, requests, tmp_path, max_tokens=None, **k
     """Every row against the plain implementation, and against the engine's own logits of the request fed whole.  A few
     positions are ill-conditioned in the design itself (a recurrent mixer's first read-outs are a vector times ONE dot
     product, whose sign and size then pass through the head norm): up to one position in fifty of a request may be off
-    by up to four times the bound against the plain implementation; against the engine itself none may."""
+    by up to four times the bound against the plain implementation (and, in bfloat16, against the engine's other kernels);
+    in float32 the engine agrees with itself at every position, however the work is cut."""
     cfg, dirs, tensors, block = folders[name]
     out = str(tmp_path / f"out_{name}_{dtype}")
     runner = traces.replay_in_process(dirs[dtype], dtype, steps, out, max_tokens or traces.live_token_peak(steps), block, **kw)
@@ -145,10 +146,11 @@ def _check(folders, name, dtype, steps, requests, tmp_path, max_tokens=None, **k
         for pos, row in sorted(got[rid].items()):
             assert np.isfinite(row).all(), f"request {rid} position {pos}: logits are not finite"
             cut = _row_error(row, whole[pos].astype(np.float64))
-            assert cut <= CUT_TOLERANCE[dtype], f"{name}/{dtype}: request {rid}: position {pos} of {len(toks)} depends on how the work was cut ({cut:.3e})"
+            sharp = dtype == "float32"          # in bfloat16 an ill-conditioned position moves with the kernels a step's size selects
+            assert cut <= CUT_TOLERANCE[dtype] * (1 if sharp else 4), f"{name}/{dtype}: request {rid}: position {pos} of {len(toks)} depends on how the work was cut ({cut:.3e})"
             err = _row_error(row, ref[pos])
             assert err <= 4 * TOLERANCE[dtype], f"{name}/{dtype}: request {rid}: first wrong position {pos} of {len(toks)} (error {err:.3e})"
-            if err > TOLERANCE[dtype]:
+            if err > TOLERANCE[dtype] or cut > CUT_TOLERANCE[dtype]:
                 over.append(pos)
             else:
                 worst = max(worst, err)
@@ -333,7 +335,7 @@ def test_routed_experts_with_the_clamped_gate(dtype, rows, width, ff, experts, t
     _close(out, want, dtype, "weighted sum of the chosen experts", tol=None if dtype == torch.float32 else 3e-2)
 
 
-def _attention_case(dtype, H, G, d, dv, lengths, new, page, seed, window, keep, cap, sharpen=None):
+def _attention_case(dtype, H, G, d, dv, lengths, new, page, seed, window, keep, cap, sharpen=None, tensor_cores=False):
     """Requests of ``lengths`` tokens whose last ``new`` are this step's queries, over a cache of random keys and values
     on shuffled pages; kernel output and the plain result from the same cached rows.  ``sharpen[t] = j`` makes query t's
     score with key j of its request stand out."""
@@ -377,8 +379,16 @@ def _attention_case(dtype, H, G, d, dv, lengths, new, page, seed, window, keep, 
             s = s.masked_fill(~seen, -math.inf)
             want[t, h] = torch.softmax(s, -1) @ kv[:, d:]
     out = torch.empty(T, H * dv, dtype=dtype, device="cuda")
-    kernels.window_attention_generic(_dev(q.reshape(T, H * d), dtype), out, cache.cuda(), table.cuda(), _ints(pos), _ints(treq),
-                                     H, G, d, dv, scale, cap or 0.0, window, keep)
+    if tensor_cores:
+        assert kernels.window_attention_mma_supports(d, dv, H, G)
+        qsl = [0]
+        for k in new:
+            qsl.append(qsl[-1] + k)
+        kernels.window_attention_mma(_dev(q.reshape(T, H * d), dtype), out, cache.cuda(), table.cuda(), _ints(qsl), _ints(lengths),
+                                     [T + 64] + [1] * (len(new) - 1), H, G, d, dv, scale, cap or 0.0, window, keep)
+    else:
+        kernels.window_attention_generic(_dev(q.reshape(T, H * d), dtype), out, cache.cuda(), table.cuda(), _ints(pos), _ints(treq),
+                                         H, G, d, dv, scale, cap or 0.0, window, keep)
     return out.view(T, H, dv), want
 
 
@@ -405,6 +415,23 @@ def test_one_key_stands_out_at_every_edge(dtype, decode):
 def test_attention_of_many_shapes(dtype, H, G, d, dv, window, keep, cap):
     got, want = _attention_case(dtype, H, G, d, dv, [50, 1, 17, 70], [50, 1, 2, 1], 16, d + window, window, keep, cap)
     _close(got, want, dtype, "attention output")
+
+
+@pytest.mark.parametrize("d,dv,H,G", [(64, 32, 4, 2), (64, 64, 8, 2), (128, 128, 2, 2), (128, 64, 6, 1), (64, 128, 4, 4), (128, 32, 2, 1)])
+def test_attention_on_the_tensor_cores(d, dv, H, G):
+    """The tensor-core kernel against plain attention over the same cached rows: windows that start inside and between
+    key tiles, kept tokens before the window, in it and none, requests of one token beside long portions, a launch
+    sized for more tiles than the batch has (a captured step's upper bound); and a key made to stand out at the
+    window's and the kept tokens' edges."""
+    dtype = torch.bfloat16
+    for window, keep, cap in ((0, 0, 0.0), (70, 9, 30.0), (64, 0, 0.0), (200, 130, 15.0), (5, 70, 0.0)):
+        got, want = _attention_case(dtype, H, G, d, dv, [300, 1, 97, 210], [300, 1, 40, 3], 16, d + dv + window, window, keep, cap,
+                                    tensor_cores=True)
+        _close(got, want, dtype, f"attention output with window {window} keeping {keep}")
+    window, keep, n = 70, 9, 260
+    for j in (n - 1 - window + 1, n - 1 - window, keep - 1, keep, 0, 63, 64, n - 1):
+        got, want = _attention_case(dtype, H, G, d, dv, [n, 50], [100, 2], 16, j, window, keep, 25.0, sharpen={99: j}, tensor_cores=True)
+        _close(got, want, dtype, f"query {n - 1} with key {j} standing out")
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
