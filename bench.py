@@ -446,16 +446,18 @@ def main() -> int:
                         help="also run the reference's serving workload (1 024-token prompts, 128 outputs, 8 and 32 requests "
                              "in flight) through the engine's continuous batching")
     parser.add_argument("--designs", action="store_true",
-                        help="instead of the benchmark: the Bilolorn design beside the Qwen3 dense decoder at equal layer sizes "
+                        help="instead of the benchmark: the Bilolorn or Kusolorn design beside the Qwen3 dense decoder at equal layer sizes "
                              "(prefill and decode throughput, every kernel of a step against its roofline; one JSON line per "
                              "design and size; see cuinfer_b200/bench_designs.py)")
     parser.add_argument("--design-sizes", default="small,large", help="with --designs: which of its sizes to run")
+    parser.add_argument("--design-names", default="bilolorn,qwen3",
+                        help="with --designs: which designs to run (bilolorn, kusolorn, qwen3)")
     args = parser.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
     if args.designs:
         from cuinfer_b200 import bench_designs
-        return bench_designs.main(["--sizes", args.design_sizes])
+        return bench_designs.main(["--sizes", args.design_sizes, "--designs", args.design_names])
     MODEL_NAME, MODEL = SHAPES[args.shape]
     if args.context != CONTEXT:
         CONTEXT = args.context

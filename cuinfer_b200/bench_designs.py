@@ -1,7 +1,8 @@
-"""Bilolorn beside the Qwen3 dense decoder at equal layer sizes: prefill and decode throughput through the model
-runner, and the time of every kernel of a step with the share of its roofline that it reaches.
+"""Bilolorn and Kusolorn beside the Qwen3 dense decoder at equal layer sizes: prefill and decode throughput through the
+model runner, and the time of every kernel of a step with the share of its roofline that it reaches.
 
-``bench.py --designs`` runs this; ``python -m cuinfer_b200.bench_designs [--sizes small,large]`` does the same.
+``bench.py --designs`` runs this (``--design-names kusolorn,qwen3`` chooses the designs);
+``python -m cuinfer_b200.bench_designs [--sizes small,large] [--designs kusolorn,qwen3]`` does the same.
 Weights are random, drawn on the device; the models have a few layers only (the figures are per step of that model;
 what is compared is one design against the other at the same sizes, and every kernel against its own roofline).
 
@@ -31,9 +32,13 @@ from . import kernels
 # decoder with the same width, head count and feed-forward size.
 SIZES = {
     "small": dict(width=1024, heads=16, dim=64, rot_dim=32, vdim=64, q_rank=512, kv_rank=256, ff=3072, experts=16, top=2,
-                  expert_ff=768, shared_ff=768, vocab=32768, layers=4, kv_heads=8, head_dim=128),
+                  expert_ff=768, shared_ff=768, vocab=32768, layers=4, kv_heads=8, head_dim=128,
+                  window=512, keep_first=4, side_dim=64, delta_heads=16, delta_kv_heads=8, delta_dim=64, delta_vdim=64,
+                  memory_heads=4, memory_dim=128, memory_vdim=256),
     "large": dict(width=4096, heads=32, dim=128, rot_dim=64, vdim=128, q_rank=1536, kv_rank=512, ff=12288, experts=32, top=2,
-                  expert_ff=1536, shared_ff=3072, vocab=32768, layers=4, kv_heads=8, head_dim=128),
+                  expert_ff=1536, shared_ff=3072, vocab=32768, layers=4, kv_heads=8, head_dim=128,
+                  window=1024, keep_first=4, side_dim=256, delta_heads=32, delta_kv_heads=16, delta_dim=128, delta_vdim=128,
+                  memory_heads=8, memory_dim=256, memory_vdim=512),
 }
 
 
@@ -46,6 +51,23 @@ def bilolorn_config(s: dict) -> dict:
     layers = [{"type": "latent_attention", "mixer": mixer, "mlp": dense if i == 0 else moe} for i in range(s["layers"])]
     return {"architecture": "Bilolorn", "architectures": ["Bilolorn"], "vocab": s["vocab"], "width": s["width"],
             "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5}, "layers": layers, "loop": {"start": 0, "stop": 0, "times": 1}}
+
+
+def kusolorn_config(s: dict) -> dict:
+    """Four layers, one of each kind and a second attention layer that mixes the first one's values in: windowed
+    attention with the Qwen3 arm's head counts and head size, the gated delta rule, the matrix memory; a dense
+    feed-forward first and routed experts after it; the per-layer token input."""
+    attention = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["head_dim"], "vdim": s["head_dim"], "scale": s["head_dim"] ** -0.5,
+                 "softcap": 50.0, "v_mix": True, "mask": {"size": s["window"], "keep_first": s["keep_first"]},
+                 "rot": {"base": 1000000.0, "dims": s["head_dim"] // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    delta = {"heads": s["delta_heads"], "kv_heads": s["delta_kv_heads"], "dim": s["delta_dim"], "vdim": s["delta_vdim"], "conv": 4}
+    memory = {"heads": s["memory_heads"], "dim": s["memory_dim"], "vdim": s["memory_vdim"], "gate_cap": 15.0}
+    dense = {"kind": "dense", "ff": s["ff"]}
+    moe = {"kind": "moe", "router": {"experts": s["experts"], "top": s["top"]}, "expert": {"ff": s["expert_ff"], "limit": 7.0}}
+    kinds = [("attention", attention, dense), ("delta", delta, moe), ("attention", attention, moe), ("mlstm", memory, moe)]
+    layers = [{"type": t, "mixer": m, "mlp": f} for t, m, f in (kinds * ((s["layers"] + 3) // 4))[:s["layers"]]]
+    return {"architecture": "Kusolorn", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6},
+            "token_side": {"dim": s["side_dim"]}, "layers": layers}
 
 
 def qwen3_config(s: dict) -> dict:
@@ -102,7 +124,7 @@ class KernelTimes:
             fn(*args, **kw)
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             rep_args = args
-            if name in ("sandwich_layernorm", "add_rmsnorm"):           # they add into their first argument
+            if name in ("sandwich_layernorm", "add_rmsnorm", "rms_stream"):           # they add into their first argument
                 rep_args = (args[0].clone(),) + tuple(args[1:])
             # the repeats are recorded into a CUDA graph and the graph is timed: the device's time, not Python's
             torch.cuda.synchronize()
@@ -127,7 +149,31 @@ class KernelTimes:
         def rowwise(*a, **kw):
             return 0.0, _nbytes(*a, *kw.values())
 
+        def windowed(q, heads, qk, v, window, keep):
+            """Attention in which a query sees at most ``window`` keys and ``keep`` kept ones: FLOPs over the visible pairs,
+            bytes of the visible rows of the cache read once per request."""
+            pairs, rows = 0, 0
+            for n, k in zip(lq, lk):
+                for p in range(k - n, k):
+                    pairs += min(p + 1, (window + keep) if window else p + 1)
+                rows += min(k, (window + keep + n) if window else k)
+            return 2.0 * pairs * heads * (qk + v), rows * (qk + v) * 2 + q.shape[0] * heads * (qk + v) * 2
+
+        def scan(tokens, heads, d, dv, per_pair, state):
+            """A recurrence over a matrix per head: ``per_pair`` operations per token and matrix element; the state is read
+            and written once, the inputs read once."""
+            return float(per_pair) * tokens * heads * d * dv, 2 * _nbytes(state) * len(lq) / max(1, state.shape[0]) + tokens * heads * (2 * d + 2 * dv) * 4
+
         costs = {
+            "rms_stream": rowwise, "gelu_tanh": rowwise, "router_topk": rowwise, "head_rms_gate": rowwise,
+            "window_attention_prep": lambda qkv, *a, **k: (0.0, 2 * _nbytes(qkv)),
+            "window_attention_generic": lambda q, out, cache, bt, pos, tr, H, G, d, dv, scale, cap, window, keep:
+                windowed(q, H, d, dv, window, keep),
+            "window_attention_mma": lambda q, out, cache, bt, qsl, sl, ql, H, G, d, dv, scale, cap, window, keep:
+                windowed(q, H, d, dv, window, keep),
+            "mlstm_scan": lambda q, k, v, gates, ib, fb, cap, qs, state, qsl, slots, out, H, d, dv, **kw: scan(out.shape[0], H, d, dv, 4, state),
+            "delta_scan": lambda qkv, gates, al, db, state, qsl, slots, out, G, H, d, dv: scan(out.shape[0], H, d, dv, 6, state),
+            "delta_prep": lambda x, taps, cs, qsl, tr, slots, G, H, d, dv, ue, qs, out: (0.0, _nbytes(out) + out.numel() * x.element_size()),
             "sandwich_layernorm": rowwise, "add_rmsnorm": rowwise, "relu_squared": rowwise, "sigmoid_gate": rowwise,
             "silu_mul": rowwise, "embedding_gather": lambda ids, table, out, *a, **k: (0.0, 2 * _nbytes(out)),
             "gather_rows": lambda res, delta, idx, out: (0.0, 2 * _nbytes(out)),
@@ -143,7 +189,7 @@ class KernelTimes:
                 _attention_cost(qkv.shape[0], nq, d, d, 2 * nkv * d * 2, lq, lk),
             "paged_attention_decode": lambda qkv, out, cache, bt, sl, nq, nkv, d, *a, **k:
                 _attention_cost(qkv.shape[0], nq, d, d, 2 * nkv * d * 2, lq, lk),
-            "moe_table_feed_forward": lambda h, ids, table, gate_up, down, base, out:
+            "moe_table_feed_forward": lambda h, ids, table, gate_up, down, base, out, **kw:
                 (2.0 * h.shape[0] * table.shape[1] * 3 * (gate_up.shape[1] // 2) * h.shape[1],
                  min(h.shape[0] * table.shape[1], gate_up.shape[0]) * 3 * (gate_up.shape[1] // 2) * h.shape[1] * 2 + 3 * _nbytes(h)),
             "gemm_generic_batched": lambda a, w, out: (2.0 * a.shape[0] * a.shape[1] * a.shape[2] * w.shape[1], _nbytes(a, w, out)),
@@ -181,7 +227,7 @@ def measure(design: str, size: str, prefill_tokens: int, batch: int, context: in
     from .engine.runner import StepEntry
 
     s = SIZES[size]
-    config = bilolorn_config(s) if design == "bilolorn" else qwen3_config(s)
+    config = {"bilolorn": bilolorn_config, "kusolorn": kusolorn_config, "qwen3": qwen3_config}[design](s)
     pages = (batch * (context + steps + 64) + prefill_tokens) // 16 + 64
     runner = make_runner(config, pages, max_seqs=max(batch, 8), graphs=True)
     gen = torch.Generator().manual_seed(5)

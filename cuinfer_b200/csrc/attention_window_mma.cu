@@ -187,7 +187,7 @@ window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, _
                 if (cap > 0.f) {
                     // cap * tanh(v / cap) = cap * (1 - 2 / (exp(2 v / cap) + 1)); the exponent is bounded so that it stays finite
                     const float x = fminf(fmaxf(2.f * v * inv_cap, -60.f), 60.f);
-                    v = cap * (1.f - 2.f / (__expf(x) + 1.f));
+                    v = cap * (1.f - __fdividef(2.f, __expf(x) + 1.f));
                 }
                 v *= kLog2e;
                 const int key = key0 + nt * 8 + quad * 2 + (e & 1);

@@ -84,9 +84,9 @@ def _declare(lib: ctypes.CDLL) -> None:
         "cib_window_attention_prep": [_P, _I, _I, _P, _P, _P, _I, _F, _I, _I, _I, _I, _P, _I, _P, _I, _P, ctypes.c_longlong, _I, _I, _P],
         "cib_window_attention_generic": [_P, _I, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _I, _P],
         "cib_window_attention_mma": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I, _P],
-        "cib_mlstm_scan": [_P, _P, _P, _I, _I, _P, _I, _P, _P, _I, _F, _F, _F, _P, _P, _P, _I, _I, _P, _I, _I, _I, _P],
+        "cib_mlstm_scan": [_P, _P, _P, _I, _I, _P, _I, _P, _P, _I, _F, _F, _F, _P, _P, _P, _I, _I, _I, _P, _I, _I, _I, _P],
         "cib_delta_prep": [_P, _I, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _P, _I, _P],
-        "cib_delta_scan": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _P, _I, _I, _P, _I, _I, _I, _P],
+        "cib_delta_scan": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I, _P, _I, _I, _I, _P],
         "cib_head_rms_gate": [_P, _P, _I, _I, _P, _I, _I, _F, _I, _P, _I, _I, _I, _P],
         "cib_router_topk": [_P, _I, _I, _I, _P, _P, _I, _P],
         "cib_rms_stream": [_P, _P, _I, _P, _I, _F, _P, _I, _F, _P, _P, _I, _I, _I, _P],
@@ -1082,7 +1082,8 @@ def mlstm_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gates: torch.T
                f_bias: torch.Tensor, cap: float, q_scale: float, state: torch.Tensor, query_start_loc: torch.Tensor,
                state_slots: torch.Tensor, out: torch.Tensor, num_heads: int, dim: int, vdim: int, floor: float = 1e-6) -> None:
     """The matrix memory with exponential gates over every request's rows, from and to its state slot.  ``q``, ``k``, ``v``
-    are column ranges of the same packed rows; ``gates`` float32 [T, 2H] (input then forget pre-activations);
+    are column ranges of the same packed rows; ``gates`` float32 [T, 2H] (input then forget pre-activations; overwritten
+    with the gates themselves by a first launch, before the scan walks the tokens);
     ``state`` float32 [slots, H, dim * vdim + dim + 1]; ``out`` float32 [T, H * vdim]."""
     T = out.shape[0]
     R = state_slots.numel()
@@ -1096,9 +1097,10 @@ def mlstm_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gates: torch.T
         _cuda(q, "q", contiguous=False), _cuda(k, "k", contiguous=False), _cuda(v, "v", contiguous=False), _code(q, "q"), q.stride(0),
         _cuda(gates, "gates", torch.float32), gates.stride(0), _cuda(i_bias, "i_bias"), _cuda(f_bias, "f_bias"), _code(i_bias, "i_bias"),
         float(cap), float(q_scale), float(floor), _cuda(state, "state", torch.float32),
-        _cuda(query_start_loc, "query_start_loc", torch.int32), _cuda(state_slots, "state_slots", torch.int32), state.shape[0], R,
+        _cuda(query_start_loc, "query_start_loc", torch.int32), _cuda(state_slots, "state_slots", torch.int32), state.shape[0], R, T,
         _cuda(out, "out", torch.float32), num_heads, dim, vdim, _stream())
     _check(rc, "mlstm_scan")
+    _count()
     _count()
 
 
@@ -1129,7 +1131,7 @@ def delta_scan(qkv: torch.Tensor, gates: torch.Tensor, a_log: torch.Tensor, dt_b
                query_start_loc: torch.Tensor, state_slots: torch.Tensor, out: torch.Tensor, num_kv_heads: int, num_heads: int,
                dim: int, vdim: int) -> None:
     """The gated delta rule over every request's rows.  ``qkv`` float32 [T, C] from ``delta_prep``; ``gates`` float32
-    [T, 2H] (beta then decay pre-activations); ``state`` float32 [slots, H, dim * vdim]; ``out`` float32 [T, H * vdim]."""
+    [T, 2H] (beta then decay pre-activations; overwritten with beta and the decay by a first launch); ``state`` float32 [slots, H, dim * vdim]; ``out`` float32 [T, H * vdim]."""
     T = qkv.shape[0]
     if state.shape[1:] != (num_heads, dim * vdim) or gates.shape != (T, 2 * num_heads) or out.shape != (T, num_heads * vdim):
         raise KernelError("delta_scan: state, gates or out do not fit")
@@ -1139,8 +1141,9 @@ def delta_scan(qkv: torch.Tensor, gates: torch.Tensor, a_log: torch.Tensor, dt_b
         _cuda(qkv, "qkv", torch.float32), num_kv_heads, _cuda(gates, "gates", torch.float32), gates.stride(0), _cuda(a_log, "a_log"),
         _cuda(dt_bias, "dt_bias"), _code(a_log, "a_log"), _cuda(state, "state", torch.float32),
         _cuda(query_start_loc, "query_start_loc", torch.int32), _cuda(state_slots, "state_slots", torch.int32), state.shape[0],
-        state_slots.numel(), _cuda(out, "out", torch.float32), num_heads, dim, vdim, _stream())
+        state_slots.numel(), T, _cuda(out, "out", torch.float32), num_heads, dim, vdim, _stream())
     _check(rc, "delta_scan")
+    _count()
     _count()
 
 
