@@ -27,30 +27,25 @@ __device__ __forceinline__ int wm_swz(int r, int c) {
     return c ^ ((r >> 1) & (CH - 1));
 }
 
+// Two threads copy one key/value row of a tile, half of its 16-byte chunks each, from the page whose number the caller
+// has looked up a tile ahead (the table lookup, the row's address and the copy are three dependent trips otherwise).
 template <int DK, int DV>
-__device__ __forceinline__ void wm_load_kv_tile(__nv_bfloat16* sK, __nv_bfloat16* sV, const __nv_bfloat16* cache,
-                                                const int* table, int key0, int key_end, int page_size, int num_pages,
-                                                int nkv, int kvh, int tid) {
-    constexpr int kCK = DK / 8, kCV = DV / 8, kC = kCK + kCV;
-    for (int idx = tid; idx < kWmN * kC; idx += kWmWarps * 32) {
-        const int row = idx / kC, chunk = idx % kC;
-        const int j = key0 + row;
-        bool valid = j < key_end;
-        int page = 0, off = 0;
-        if (valid) {
-            page = table[j / page_size];
-            off = j % page_size;
-            valid = page >= 0 && page < num_pages;
-        }
-        const __nv_bfloat16* src = cache + (((size_t)(valid ? page : 0) * nkv + kvh) * page_size + (valid ? off : 0)) * (DK + DV) + chunk * 8;
+__device__ __forceinline__ void wm_load_kv_row(__nv_bfloat16* sK, __nv_bfloat16* sV, const __nv_bfloat16* cache, int page, int j,
+                                               int page_size, int num_pages, int nkv, int kvh, int row, int half) {
+    constexpr int kCK = DK / 8, kCV = DV / 8, kC = kCK + kCV, kHalf = kC / 2;
+    const bool valid = page >= 0 && page < num_pages;
+    const __nv_bfloat16* src = cache + (((size_t)(valid ? page : 0) * nkv + kvh) * page_size + (valid ? j % page_size : 0)) * (DK + DV);
+#pragma unroll
+    for (int c = 0; c < kHalf; ++c) {
+        const int chunk = half * kHalf + c;
         __nv_bfloat16* dst = chunk < kCK ? sK + row * DK + wm_swz<kCK>(row, chunk) * 8
                                          : sV + row * DV + wm_swz<kCV>(row, chunk - kCK) * 8;
-        cp_async16(dst, src, valid);
+        cp_async16(dst, src + chunk * 8, valid);
     }
 }
 
 template <int DK, int DV>
-__global__ void __launch_bounds__(kWmWarps * 32, 2)
+__global__ void __launch_bounds__(kWmWarps * 32, 3)
 window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* __restrict__ out,
                             int out_stride, const __nv_bfloat16* __restrict__ cache, int num_pages, int page_size,
                             const int* __restrict__ block_table, int table_stride,
@@ -103,6 +98,19 @@ window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, _
     const int num_tiles = kept_tiles + (k_hi - k_lo + kWmN - 1) / kWmN;
     auto tile_key0 = [&](int t) { return t < kept_tiles ? t * kWmN : k_lo + (t - kept_tiles) * kWmN; };
     auto tile_end = [&](int t) { return t < kept_tiles ? kept_end : k_hi; };
+    // this thread's key row of every tile, and the page that holds it (-1: past the tile's end, or no such tile)
+    const int my_row = tid >> 1, my_half = tid & 1;
+    auto lookup = [&](int t) {
+        if (t >= num_tiles) return -1;
+        const int j = tile_key0(t) + my_row;
+        return j < tile_end(t) ? table[j / page_size] : -1;
+    };
+    auto load_tile = [&](int t, int page) {
+        wm_load_kv_row<DK, DV>(stage_k(t % kWmStages), stage_v(t % kWmStages), cache, page, tile_key0(t) + my_row, page_size,
+                               num_pages, nkv, kvh, my_row, my_half);
+    };
+    const int page_first = lookup(0);
+    int page_next = lookup(1);
 
     {
         for (int idx = tid; idx < kWmM * kCK; idx += kWmWarps * 32) {
@@ -115,7 +123,7 @@ window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, _
         }
         cp_async_commit();
     }
-    wm_load_kv_tile<DK, DV>(stage_k(0), stage_v(0), cache, table, tile_key0(0), tile_end(0), page_size, num_pages, nkv, kvh, tid);
+    load_tile(0, page_first);
     cp_async_commit();
 
     cp_async_wait<1>();
@@ -140,6 +148,13 @@ window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, _
         pos_row[h] = row_ok[h] ? seq_len - n + grow / g : -1;
     }
 
+    // first and last position among this warp's rows: a key tile that every one of them sees whole needs no mask
+    const int warp_row_first = row0 + warp * 16, warp_row_last = min(row0 + warp * 16 + 15, rows_total - 1);
+    const bool warp_has_rows = warp_row_first < rows_total;
+    const int warp_pos_min = seq_len - n + (warp_has_rows ? warp_row_first : 0) / g;
+    const int warp_pos_max = seq_len - n + (warp_has_rows ? warp_row_last : 0) / g;
+    const bool warp_full = warp_row_first + 15 < rows_total;      // no row of the warp is padding
+
     float o[DV / 8][4];
 #pragma unroll
     for (int i = 0; i < DV / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
@@ -150,10 +165,9 @@ window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, _
     for (int t = 0; t < num_tiles; ++t) {
         const int key0 = tile_key0(t);
         const bool kept_tile = t < kept_tiles;
-        if (t + 1 < num_tiles)
-            wm_load_kv_tile<DK, DV>(stage_k((t + 1) % kWmStages), stage_v((t + 1) % kWmStages), cache, table, tile_key0(t + 1),
-                                    tile_end(t + 1), page_size, num_pages, nkv, kvh, tid);
+        if (t + 1 < num_tiles) load_tile(t + 1, page_next);
         cp_async_commit();
+        page_next = lookup(t + 2);
         cp_async_wait<1>();
         __syncthreads();
         const __nv_bfloat16* sK = stage_k(t % kWmStages);
@@ -177,6 +191,8 @@ window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, _
                 }
             }
         }
+        const bool need_mask = !warp_full || (kept_tile ? key0 + kWmN > kept_end
+                                                        : (key0 + kWmN - 1 > warp_pos_min || (window > 0 && key0 <= warp_pos_max - window)));
         float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
         for (int nt = 0; nt < kWmN / 8; ++nt) {
@@ -190,11 +206,13 @@ window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, _
                     v = cap * (1.f - __fdividef(2.f, __expf(x) + 1.f));
                 }
                 v *= kLog2e;
-                const int key = key0 + nt * 8 + quad * 2 + (e & 1);
-                const int pos = pos_row[h];
-                const bool vis = kept_tile ? (key < kept_end && pos >= 0)
-                                           : (key <= pos && (window <= 0 || key > pos - window || key < keep_first));
-                v = vis ? v : -INFINITY;
+                if (need_mask) {
+                    const int key = key0 + nt * 8 + quad * 2 + (e & 1);
+                    const int pos = pos_row[h];
+                    const bool vis = kept_tile ? (key < kept_end && pos >= 0)
+                                               : (key <= pos && (window <= 0 || key > pos - window || key < keep_first));
+                    v = vis ? v : -INFINITY;
+                }
                 s[nt][e] = v;
                 mx[h] = fmaxf(mx[h], v);
             }
