@@ -590,3 +590,87 @@ def test_delta_rule_through_portions_and_slots(dtype, H, G, d, dv, K):
     for r in range(2):
         want = plain.delta_mixer(feats[r], w, cfg, 1e-5)
         _close(got[r], want, dtype, f"request {r}", tol=1e-4 if dtype == torch.float32 else 2e-2)
+
+
+# ---- other sizes, drawn at random ---------------------------------------------------------------------------------------
+def _random_config(seed):
+    """A small configuration whose every size, count, constant and the order of its layers is drawn: odd and even sizes,
+    ones, absent parts (no window, no cap, no rotation, no scaling, no feed-forward, no per-layer token input)."""
+    import random
+
+    rnd = random.Random(seed)
+    width = rnd.choice([24, 40, 56, 64, 100])
+    vocab = rnd.choice([33, 64, 131])
+    mix_heads, mix_vdim = rnd.choice([1, 2, 3]), rnd.choice([4, 8, 20, 32])      # layers that mix values agree in these
+
+    def feed_forward():
+        kind = rnd.choice(["dense", "moe", "moe", None])
+        if kind == "dense":
+            return {"kind": "dense", "ff": rnd.choice([16, 40, 96])}
+        if kind == "moe":
+            experts = rnd.randint(2, 6)
+            return _moe(experts, rnd.randint(1, experts), rnd.choice([8, 16, 32]), rnd.choice([0.5, 1.0, 7.0]))
+        return None
+
+    layers = []
+    for _ in range(rnd.randint(2, 5)):
+        kind = rnd.choice(["attention", "attention", "mlstm", "delta"])
+        if kind == "attention":
+            v_mix = rnd.random() < 0.6
+            kv = mix_heads if v_mix else rnd.choice([1, 2, 4])
+            dim = rnd.choice([8, 12, 16, 20, 32, 64])
+            rot = None
+            if rnd.random() < 0.8:
+                rot = {"base": rnd.choice([50.0, 1e4, 1e6]), "dims": rnd.choice([2, 4, dim // 4 * 2, dim // 2 * 2])}
+                if rnd.random() < 0.5:
+                    rot["scaling"] = {"factor": rnd.choice([2.0, 8.0]), "low": 1.0, "high": rnd.choice([2.0, 4.0]), "original": rnd.choice([16, 64, 512])}
+            window = rnd.choice([None, 1, 3, 8, 16, 33, 64])
+            layers.append(_attention(kv * rnd.choice([1, 2, 4]), kv, dim, mix_vdim if v_mix else rnd.choice([4, 8, 16, 20, 32]),
+                                     rnd.choice([0.5, 1.0, 2.0]) / math.sqrt(dim), window=window, keep=rnd.choice([0, 1, 4, 20]), rot=rot,
+                                     softcap=rnd.choice([None, 5.0, 30.0]), v_mix=v_mix, mlp=feed_forward()))
+        elif kind == "mlstm":
+            layers.append({"type": "mlstm", "mixer": {"heads": rnd.randint(1, 4), "dim": rnd.choice([4, 12, 16, 33, 48]),
+                                                      "vdim": rnd.choice([8, 16, 24, 40]), "gate_cap": rnd.choice([5.0, 15.0])}, "mlp": feed_forward()})
+        else:
+            kv = rnd.randint(1, 3)
+            layers.append({"type": "delta", "mixer": {"heads": kv * rnd.choice([1, 2]), "kv_heads": kv, "dim": rnd.choice([4, 8, 16, 24, 40]),
+                                                      "vdim": rnd.choice([8, 12, 16, 32]), "conv": rnd.randint(1, 5)}, "mlp": feed_forward()})
+    return _config(vocab, width, layers, side=rnd.choice([None, 2, 6, 10]), eps=rnd.choice([1e-6, 1e-5, 1e-3])), rnd.choice([16, 32])
+
+
+@pytest.mark.parametrize("seed", range(10))
+def test_configurations_drawn_at_random(seed, tmp_path):
+    cfg, page = _random_config(seed)
+    tensors = plain.random_model(cfg, 100 + seed)
+    t64 = {k: v.double() for k, v in tensors.items()}
+    requests = _requests(cfg, [1, 23, 70, 9], seed=30 + seed)
+    steps = traces.mixed(requests, max_live=3, sizes=(5, 2, 11, 3))
+    refs = {}
+    for rid, toks in requests.items():
+        assert plain.router_margin(cfg, t64, list(toks)) > 0.03, "the drawn routers must not rest on a close call"
+        refs[rid] = plain.forward(cfg, t64, list(toks)).numpy()
+    for dtype in ("float32", "bfloat16"):
+        folder = _write(str(tmp_path / dtype), cfg, tensors, dtype)
+        out = str(tmp_path / f"out_{dtype}")
+        traces.replay_in_process(folder, dtype, steps, out, traces.live_token_peak(steps), page, max_live=4)
+        got = traces.collect(steps, out, cfg["vocab"])
+        whole_steps = traces.whole(requests)
+        whole_out = str(tmp_path / f"whole_{dtype}")
+        traces.replay_in_process(folder, dtype, whole_steps, whole_out, traces.live_token_peak(whole_steps), page)
+        whole = traces.collect(whole_steps, whole_out, cfg["vocab"])
+        errors = []
+        for rid, toks in requests.items():
+            for pos, row in sorted(got[rid].items()):
+                assert np.isfinite(row).all()
+                errors.append((_row_error(row, refs[rid][pos]), rid, pos))
+                if dtype == "float32":
+                    cut = _row_error(row, whole[rid][pos].astype(np.float64))
+                    assert cut <= CUT_TOLERANCE[dtype], f"configuration {seed}: request {rid} position {pos} depends on the cut ({cut:.3e}): {json.dumps(cfg)}"
+        # float32 is held row by row, but for the few positions that the design itself conditions badly (see _check); the
+        # bfloat16 run of these very narrow layers is held by its median row, which a wrong shape or kernel choice would move
+        ranked = sorted(errors)
+        if dtype == "float32":
+            assert ranked[int(0.97 * len(ranked))][0] <= TOLERANCE[dtype] and ranked[-1][0] <= 25 * TOLERANCE[dtype], \
+                f"configuration {seed}: request {ranked[-1][1]} position {ranked[-1][2]} (error {ranked[-1][0]:.3e}): {json.dumps(cfg)}"
+        else:
+            assert ranked[len(ranked) // 2][0] <= 0.05, f"configuration {seed} in bfloat16: median row error {ranked[len(ranked) // 2][0]:.3e}: {json.dumps(cfg)}"
