@@ -46,6 +46,8 @@ class WindowAttention(Mixer):
         self.vdim = int(spec.vdim)
         if self.num_heads <= 0 or self.num_kv_heads <= 0 or self.num_heads % self.num_kv_heads:
             raise ValueError("window_attention: num_heads must be a positive multiple of num_kv_heads")
+        if not (0 < self.dim <= 512 and 0 < self.vdim <= 512):
+            raise ValueError(f"window_attention: key size {self.dim} / value size {self.vdim} are beyond what the kernels take (512)")
         self.scale = float(spec.scale)
         self.softcap = float(spec.get("softcap") or 0.0)
         self.window = int(spec.get("window") or 0)
