@@ -103,6 +103,8 @@ class GeluFeedForward(SquaredReluFeedForward):
     """``down( gelu_tanh(up(x)) )`` with the tanh form of GELU, no gate, no biases.  Spec: ``PartSpec("gelu_tanh",
     intermediate_size=I, names=(up, down))``."""
 
+    accepts_lazy_norm = True       # the up projection can compute the norm of its input itself
+
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         y = self.up.forward(x)
         act = torch.empty_like(y)

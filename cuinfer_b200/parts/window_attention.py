@@ -38,6 +38,8 @@ VALUE_MIX_KEY = "window_attention.values"
 
 @MIXERS.register("window_attention")
 class WindowAttention(Mixer):
+    accepts_lazy_norm = True       # the q/k/v projection can compute the norm of its input itself
+
     def __init__(self, spec: PartSpec, *, hidden_size: int, prefix: str, dtype: torch.dtype) -> None:
         super().__init__(spec, hidden_size=hidden_size, prefix=prefix, dtype=dtype)
         self.num_heads = int(spec.num_heads)
