@@ -594,22 +594,25 @@ def test_delta_rule_through_portions_and_slots(dtype, H, G, d, dv, K):
 
 # ---- other sizes, drawn at random ---------------------------------------------------------------------------------------
 def _random_config(seed):
-    """A small configuration whose every size, count, constant and the order of its layers is drawn: odd and even sizes,
-    ones, absent parts (no window, no cap, no rotation, no scaling, no feed-forward, no per-layer token input)."""
+    """A small configuration whose every size, count, constant and the order of its layers is drawn: ones, absent parts
+    (no window, no cap, no rotation, no scaling, no feed-forward, no per-layer token input); from seed 10 on every size
+    is odd or at least no multiple of eight."""
     import random
 
     rnd = random.Random(seed)
-    width = rnd.choice([24, 40, 56, 64, 100])
-    vocab = rnd.choice([33, 64, 131])
-    mix_heads, mix_vdim = rnd.choice([1, 2, 3]), rnd.choice([4, 8, 20, 32])      # layers that mix values agree in these
+    odd = seed >= 10
+    pick = lambda even_sizes, odd_sizes: rnd.choice(odd_sizes if odd else even_sizes)      # noqa: E731
+    width = pick([24, 40, 56, 64, 100], [37, 50, 66, 98, 131])
+    vocab = pick([33, 64, 131], [31, 77, 257])
+    mix_heads, mix_vdim = pick([1, 2, 3], [1, 2, 5]), pick([4, 8, 20, 32], [3, 7, 10, 33])      # layers that mix values agree in these
 
     def feed_forward():
         kind = rnd.choice(["dense", "moe", "moe", None])
         if kind == "dense":
-            return {"kind": "dense", "ff": rnd.choice([16, 40, 96])}
+            return {"kind": "dense", "ff": pick([16, 40, 96], [15, 41, 99])}
         if kind == "moe":
             experts = rnd.randint(2, 6)
-            return _moe(experts, rnd.randint(1, experts), rnd.choice([8, 16, 32]), rnd.choice([0.5, 1.0, 7.0]))
+            return _moe(experts, rnd.randint(1, experts), pick([8, 16, 32], [7, 18, 33]), rnd.choice([0.5, 1.0, 7.0]))
         return None
 
     layers = []
@@ -617,28 +620,28 @@ def _random_config(seed):
         kind = rnd.choice(["attention", "attention", "mlstm", "delta"])
         if kind == "attention":
             v_mix = rnd.random() < 0.6
-            kv = mix_heads if v_mix else rnd.choice([1, 2, 4])
-            dim = rnd.choice([8, 12, 16, 20, 32, 64])
+            kv = mix_heads if v_mix else pick([1, 2, 4], [1, 3, 5])
+            dim = pick([8, 12, 16, 20, 32, 64], [6, 7, 9, 14, 22, 50])
             rot = None
             if rnd.random() < 0.8:
                 rot = {"base": rnd.choice([50.0, 1e4, 1e6]), "dims": rnd.choice([2, 4, dim // 4 * 2, dim // 2 * 2])}
                 if rnd.random() < 0.5:
                     rot["scaling"] = {"factor": rnd.choice([2.0, 8.0]), "low": 1.0, "high": rnd.choice([2.0, 4.0]), "original": rnd.choice([16, 64, 512])}
-            window = rnd.choice([None, 1, 3, 8, 16, 33, 64])
-            layers.append(_attention(kv * rnd.choice([1, 2, 4]), kv, dim, mix_vdim if v_mix else rnd.choice([4, 8, 16, 20, 32]),
-                                     rnd.choice([0.5, 1.0, 2.0]) / math.sqrt(dim), window=window, keep=rnd.choice([0, 1, 4, 20]), rot=rot,
+            window = pick([None, 1, 3, 8, 16, 33, 64], [None, 1, 2, 7, 15, 31, 65])
+            layers.append(_attention(kv * pick([1, 2, 4], [1, 2, 3]), kv, dim, mix_vdim if v_mix else pick([4, 8, 16, 20, 32], [5, 9, 17, 40]),
+                                     rnd.choice([0.5, 1.0, 2.0]) / math.sqrt(dim), window=window, keep=pick([0, 1, 4, 20], [0, 1, 3, 17]), rot=rot,
                                      softcap=rnd.choice([None, 5.0, 30.0]), v_mix=v_mix, mlp=feed_forward()))
         elif kind == "mlstm":
-            layers.append({"type": "mlstm", "mixer": {"heads": rnd.randint(1, 4), "dim": rnd.choice([4, 12, 16, 33, 48]),
-                                                      "vdim": rnd.choice([8, 16, 24, 40]), "gate_cap": rnd.choice([5.0, 15.0])}, "mlp": feed_forward()})
+            layers.append({"type": "mlstm", "mixer": {"heads": rnd.randint(1, 4), "dim": pick([4, 12, 16, 33, 48], [3, 11, 31, 65, 129]),
+                                                      "vdim": pick([8, 16, 24, 40], [5, 17, 33, 70]), "gate_cap": rnd.choice([5.0, 15.0])}, "mlp": feed_forward()})
         else:
             kv = rnd.randint(1, 3)
-            layers.append({"type": "delta", "mixer": {"heads": kv * rnd.choice([1, 2]), "kv_heads": kv, "dim": rnd.choice([4, 8, 16, 24, 40]),
-                                                      "vdim": rnd.choice([8, 12, 16, 32]), "conv": rnd.randint(1, 5)}, "mlp": feed_forward()})
-    return _config(vocab, width, layers, side=rnd.choice([None, 2, 6, 10]), eps=rnd.choice([1e-6, 1e-5, 1e-3])), rnd.choice([16, 32])
+            layers.append({"type": "delta", "mixer": {"heads": kv * pick([1, 2], [1, 3]), "kv_heads": kv, "dim": pick([4, 8, 16, 24, 40], [3, 9, 33, 70]),
+                                                      "vdim": pick([8, 12, 16, 32], [5, 13, 31, 66]), "conv": rnd.randint(1, 5)}, "mlp": feed_forward()})
+    return _config(vocab, width, layers, side=pick([None, 2, 6, 10], [None, 1, 5, 9]), eps=rnd.choice([1e-6, 1e-5, 1e-3])), pick([16, 32], [16, 32, 64])
 
 
-@pytest.mark.parametrize("seed", range(10))
+@pytest.mark.parametrize("seed", range(16))
 def test_configurations_drawn_at_random(seed, tmp_path):
     cfg, page = _random_config(seed)
     tensors = plain.random_model(cfg, 100 + seed)
