@@ -169,7 +169,7 @@ class KernelTimes:
             "window_attention_prep": lambda qkv, *a, **k: (0.0, 2 * _nbytes(qkv)),
             "window_attention_generic": lambda q, out, cache, bt, pos, tr, H, G, d, dv, scale, cap, window, keep:
                 windowed(q, H, d, dv, window, keep),
-            "window_attention_mma": lambda q, out, cache, bt, qsl, sl, ql, H, G, d, dv, scale, cap, window, keep:
+            "window_attention_mma": lambda q, out, cache, bt, qsl, sl, ql, H, G, d, dv, scale, cap, window, keep, **kw:
                 windowed(q, H, d, dv, window, keep),
             "mlstm_scan": lambda q, k, v, gates, ib, fb, cap, qs, state, qsl, slots, out, H, d, dv, **kw: scan(out.shape[0], H, d, dv, 4, state),
             "delta_scan": lambda qkv, gates, al, db, state, qsl, slots, out, G, H, d, dv: scan(out.shape[0], H, d, dv, 6, state),

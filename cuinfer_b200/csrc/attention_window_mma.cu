@@ -50,7 +50,8 @@ window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, _
                             int out_stride, const __nv_bfloat16* __restrict__ cache, int num_pages, int page_size,
                             const int* __restrict__ block_table, int table_stride,
                             const int* __restrict__ query_start_loc, const int* __restrict__ seq_lens,
-                            int num_requests, int nq, int nkv, float scale, float cap, int window, int keep_first) {
+                            int num_requests, int nq, int nkv, float scale, float cap, int window, int keep_first,
+                            int num_splits, float* __restrict__ partial) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ int s_req, s_tile;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -98,19 +99,23 @@ window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, _
     const int num_tiles = kept_tiles + (k_hi - k_lo + kWmN - 1) / kWmN;
     auto tile_key0 = [&](int t) { return t < kept_tiles ? t * kWmN : k_lo + (t - kept_tiles) * kWmN; };
     auto tile_end = [&](int t) { return t < kept_tiles ? kept_end : k_hi; };
+    // with several splits (decode steps over long windows) this CTA walks a share of the key tiles and leaves its
+    // running maximum, sum and unnormalised output for the merge kernel
+    const int t_begin = (int)((long long)num_tiles * blockIdx.z / num_splits);
+    const int t_end = (int)((long long)num_tiles * (blockIdx.z + 1) / num_splits);
     // this thread's key row of every tile, and the page that holds it (-1: past the tile's end, or no such tile)
     const int my_row = tid >> 1, my_half = tid & 1;
     auto lookup = [&](int t) {
-        if (t >= num_tiles) return -1;
+        if (t >= t_end) return -1;
         const int j = tile_key0(t) + my_row;
         return j < tile_end(t) ? table[j / page_size] : -1;
     };
     auto load_tile = [&](int t, int page) {
-        wm_load_kv_row<DK, DV>(stage_k(t % kWmStages), stage_v(t % kWmStages), cache, page, tile_key0(t) + my_row, page_size,
+        wm_load_kv_row<DK, DV>(stage_k((t - t_begin) % kWmStages), stage_v((t - t_begin) % kWmStages), cache, page, tile_key0(t) + my_row, page_size,
                                num_pages, nkv, kvh, my_row, my_half);
     };
-    const int page_first = lookup(0);
-    int page_next = lookup(1);
+    const int page_first = lookup(t_begin);
+    int page_next = lookup(t_begin + 1);
 
     {
         for (int idx = tid; idx < kWmM * kCK; idx += kWmWarps * 32) {
@@ -123,7 +128,7 @@ window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, _
         }
         cp_async_commit();
     }
-    load_tile(0, page_first);
+    if (t_begin < t_end) load_tile(t_begin, page_first);
     cp_async_commit();
 
     cp_async_wait<1>();
@@ -162,16 +167,16 @@ window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, _
     float l_run[2] = {0.f, 0.f};
     const float inv_cap = cap > 0.f ? 1.f / cap : 0.f;
 
-    for (int t = 0; t < num_tiles; ++t) {
+    for (int t = t_begin; t < t_end; ++t) {
         const int key0 = tile_key0(t);
         const bool kept_tile = t < kept_tiles;
-        if (t + 1 < num_tiles) load_tile(t + 1, page_next);
+        if (t + 1 < t_end) load_tile(t + 1, page_next);
         cp_async_commit();
         page_next = lookup(t + 2);
         cp_async_wait<1>();
         __syncthreads();
-        const __nv_bfloat16* sK = stage_k(t % kWmStages);
-        const __nv_bfloat16* sV = stage_v(t % kWmStages);
+        const __nv_bfloat16* sK = stage_k((t - t_begin) % kWmStages);      // the first tile of a CTA goes to stage 0: the queries borrow stage 1
+        const __nv_bfloat16* sV = stage_v((t - t_begin) % kWmStages);
 
         float s[kWmN / 8][4];
 #pragma unroll
@@ -272,6 +277,19 @@ window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, _
         const float inv = l > 0.f ? 1.f / l : 0.f;
         const int grow = row0 + warp * 16 + qrow + 8 * h;
         const int tl = grow / g, hi = grow % g;
+        if (num_splits > 1) {
+            float* dst = partial + (((size_t)(q0 + tl) * nq + kvh * g + hi) * num_splits + blockIdx.z) * (DV + 2);
+#pragma unroll
+            for (int nt = 0; nt < DV / 8; ++nt) {
+                dst[nt * 8 + quad * 2] = o[nt][2 * h];
+                dst[nt * 8 + quad * 2 + 1] = o[nt][2 * h + 1];
+            }
+            if (quad == 0) {
+                dst[DV] = m_run[h];
+                dst[DV + 1] = l;
+            }
+            continue;
+        }
         __nv_bfloat16* dst = out + (size_t)(q0 + tl) * out_stride + (size_t)(kvh * g + hi) * DV;
 #pragma unroll
         for (int nt = 0; nt < DV / 8; ++nt) {
@@ -280,19 +298,51 @@ window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, _
     }
 }
 
+// out[row] = sum_i o_i 2^(m_i - M) / sum_i l_i 2^(m_i - M) over the splits' partial results; a warp per (token, head).
+__global__ void window_attention_merge_kernel(const float* __restrict__ partial, int num_splits, int dv,
+                                              __nv_bfloat16* __restrict__ out, int out_stride, int nq, int rows) {
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const float* base = partial + (size_t)row * num_splits * (dv + 2);
+    float M = -INFINITY;
+    for (int i = 0; i < num_splits; ++i) M = fmaxf(M, base[(size_t)i * (dv + 2) + dv]);
+    float L = 0.f;
+    for (int i = 0; i < num_splits; ++i) {
+        const float mi = base[(size_t)i * (dv + 2) + dv];
+        if (mi != -INFINITY) L += base[(size_t)i * (dv + 2) + dv + 1] * exp2f(mi - M);
+    }
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+    __nv_bfloat16* dst = out + (size_t)(row / nq) * out_stride + (size_t)(row % nq) * dv;
+    for (int c = lane; c < dv; c += 32) {
+        float acc = 0.f;
+        for (int i = 0; i < num_splits; ++i) {
+            const float mi = base[(size_t)i * (dv + 2) + dv];
+            if (mi != -INFINITY) acc = fmaf(base[(size_t)i * (dv + 2) + c], exp2f(mi - M), acc);
+        }
+        dst[c] = __float2bfloat16_rn(acc * inv);
+    }
+}
+
 template <int DK, int DV>
 static int launch_window_mma(const void* q, int q_stride, void* out, int out_stride, const void* cache, int num_pages,
                              int page_size, const int* block_table, int table_stride, const int* query_start_loc,
                              const int* seq_lens, int num_requests, int num_tiles, int nq, int nkv, float scale, float cap,
-                             int window, int keep_first, cudaStream_t stream) {
+                             int window, int keep_first, int num_splits, float* partial, int num_tokens, cudaStream_t stream) {
     const size_t smem = (size_t)(kWmStages * kWmN * (DK + DV)) * sizeof(__nv_bfloat16);
     static SmemLimit limit;
     if (int rc = raise_smem_limit(limit, window_attention_mma_kernel<DK, DV>, smem, "window_attention_mma")) return rc;
-    dim3 grid(num_tiles, nkv);
+    dim3 grid(num_tiles, nkv, num_splits);
     window_attention_mma_kernel<DK, DV><<<grid, kWmWarps * 32, smem, stream>>>(
         (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)cache, num_pages,
-        page_size, block_table, table_stride, query_start_loc, seq_lens, num_requests, nq, nkv, scale, cap, window, keep_first);
+        page_size, block_table, table_stride, query_start_loc, seq_lens, num_requests, nq, nkv, scale, cap, window, keep_first,
+        num_splits, partial);
     CIB_LAUNCH_CHECK("window_attention_mma");
+    if (num_splits > 1) {
+        const int rows = num_tokens * nq;
+        window_attention_merge_kernel<<<(rows + 7) / 8, 256, 0, stream>>>(partial, num_splits, DV, (__nv_bfloat16*)out, out_stride, nq, rows);
+        CIB_LAUNCH_CHECK("window_attention_merge");
+    }
     return 0;
 }
 
@@ -305,14 +355,16 @@ extern "C" int cib_window_attention_mma_supports(int dim, int vdim, int nq, int 
 }
 
 // num_tiles: the sum over requests of ceil(tokens_r * (nq / nkv) / 64), or any upper bound of it (CTAs that find no
-// tile leave).
+// tile leave).  num_splits > 1: every row tile's key tiles are shared out to so many CTAs, which leave float32 partial
+// results in `partial` ([tokens * nq][num_splits][vdim + 2]: output, running maximum, sum) for a second kernel to merge.
 extern "C" int cib_window_attention_mma(const void* q, int q_stride, void* out, int out_stride, const void* cache,
                                         int num_pages, int page_size, const int* block_table, int table_stride,
                                         const int* query_start_loc, const int* seq_lens, int num_requests, int num_tiles,
                                         int nq, int nkv, int dim, int vdim, float scale, float cap, int window,
-                                        int keep_first, cudaStream_t stream) {
+                                        int keep_first, int num_splits, float* partial, int num_tokens, cudaStream_t stream) {
     CIB_REQUIRE(cib_window_attention_mma_supports(dim, vdim, nq, nkv), "window_attention_mma: sizes %d / %d are not taken by this kernel", dim, vdim);
     CIB_REQUIRE(num_requests >= 0 && num_tiles >= 0 && nkv <= 65535, "window_attention_mma: bad sizes");
+    CIB_REQUIRE(num_splits >= 1 && num_splits <= 64 && (num_splits == 1 || partial), "window_attention_mma: %d splits need room for their partial results", num_splits);
     CIB_REQUIRE(page_size > 0 && num_pages > 0 && table_stride > 0 && window >= 0 && keep_first >= 0, "window_attention_mma: bad cache geometry");
     CIB_REQUIRE(q_stride % 8 == 0 && ((uintptr_t)q % 16) == 0 && out_stride % 2 == 0 && ((uintptr_t)out % 4) == 0 && ((uintptr_t)cache % 16) == 0,
                 "window_attention_mma: q and cache rows must be 16-byte aligned and out rows 4-byte aligned");
@@ -321,7 +373,7 @@ extern "C" int cib_window_attention_mma(const void* q, int q_stride, void* out, 
     if (dim == DKv && vdim == DVv)                                                                                           \
         return launch_window_mma<DKv, DVv>(q, q_stride, out, out_stride, cache, num_pages, page_size, block_table, table_stride, \
                                            query_start_loc, seq_lens, num_requests, num_tiles, nq, nkv, scale, cap, window,     \
-                                           keep_first, stream)
+                                           keep_first, num_splits, partial, num_tokens, stream)
     CIB_WM(64, 32);
     CIB_WM(64, 64);
     CIB_WM(64, 128);

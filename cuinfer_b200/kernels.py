@@ -83,7 +83,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "cib_moe_table_down": [_P, _I, _P, _P, _I, _I, _I, _P, _P, _I, _F, _P, _P, _I, _I, _I, _P],
         "cib_window_attention_prep": [_P, _I, _I, _P, _P, _P, _I, _F, _I, _I, _I, _I, _P, _I, _P, _I, _P, ctypes.c_longlong, _I, _I, _P],
         "cib_window_attention_generic": [_P, _I, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _I, _P],
-        "cib_window_attention_mma": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I, _P],
+        "cib_window_attention_mma": [_P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I, _I, _P, _I, _P],
         "cib_mlstm_scan": [_P, _P, _P, _I, _I, _P, _I, _P, _P, _I, _F, _F, _F, _P, _P, _P, _I, _I, _I, _P, _I, _I, _I, _P],
         "cib_delta_prep": [_P, _I, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _P, _I, _P],
         "cib_delta_scan": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I, _P, _I, _I, _I, _P],
@@ -1058,22 +1058,28 @@ def window_attention_mma_supports(dim: int, vdim: int, num_heads: int, num_kv_he
 
 def window_attention_mma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                          query_start_loc: torch.Tensor, seq_lens: torch.Tensor, query_lens, num_heads: int, num_kv_heads: int,
-                         dim: int, vdim: int, scale: float, softcap: float, window: int, keep_first: int) -> None:
+                         dim: int, vdim: int, scale: float, softcap: float, window: int, keep_first: int, splits: int = 1) -> None:
     """The same attention on the tensor cores (bfloat16; key sizes 64 or 128, value sizes 32, 64 or 128).  ``query_lens``:
     tokens per request as host integers, or an upper bound that holds for every batch a captured step replays; they size
-    the launch only."""
+    the launch only.  ``splits`` > 1: the key tiles of every row tile are shared out to so many CTAs and a second kernel
+    merges their partial results (decode steps over long windows, where a request has one row tile per key head)."""
     T = q.shape[0]
     if q.dtype != torch.bfloat16 or q.stride(1) != 1 or out.shape != (T, num_heads * vdim) or out.dtype != q.dtype or cache.dtype != q.dtype:
         raise KernelError("window_attention_mma: bfloat16 rows, out [T, H * vdim]")
     g = num_heads // num_kv_heads
     tiles = sum((n * g + 63) // 64 for n in query_lens)
+    splits = max(1, min(int(splits), 64))
+    partial = torch.empty((T * num_heads, splits, vdim + 2), dtype=torch.float32, device=q.device) if splits > 1 else None
     rc = library().cib_window_attention_mma(
         _cuda(q, "q", contiguous=False), q.stride(0), _cuda(out, "out"), out.stride(0), _cuda(cache, "cache"), cache.shape[0],
         cache.shape[3], _cuda(block_table, "block_table", torch.int32, contiguous=False), block_table.stride(0),
         _cuda(query_start_loc, "query_start_loc", torch.int32), _cuda(seq_lens, "seq_lens", torch.int32), seq_lens.numel(), tiles,
-        num_heads, num_kv_heads, dim, vdim, float(scale), float(softcap or 0.0), int(window or 0), int(keep_first or 0), _stream())
+        num_heads, num_kv_heads, dim, vdim, float(scale), float(softcap or 0.0), int(window or 0), int(keep_first or 0), splits,
+        _cuda(partial, "partial") if partial is not None else None, T, _stream())
     _check(rc, "window_attention_mma")
     _count()
+    if splits > 1:
+        _count()
 
 
 # ---- mixers with a matrix state ------------------------------------------------------------------------------------------------

@@ -75,20 +75,35 @@ def latent_attention(q_abs: torch.Tensor, q: torch.Tensor, out: torch.Tensor, kv
                                      ctx.token_request, ctx.positions, freq, rot_dims, sinks, num_heads, dn, rk, dr, scale, window)
 
 
+def window_decode_splits(ctx: StepContext, num_kv_heads: int, window: int, keep_first: int) -> int:
+    """Over how many CTAs a decode step shares the key tiles of a (request, key head): one CTA walks them one after the
+    other otherwise, and a step of few requests leaves most SMs idle.  At least two tiles a CTA, at most eight splits,
+    and no more CTAs than two a SM."""
+    if not ctx.decode_only:
+        return 1
+    keys = max(1, ctx.max_seq_len)
+    if window:
+        keys = min(keys, window + 63) + (64 if keep_first else 0)
+    tiles = -(-keys // 64)
+    ctas = max(1, ctx.num_requests * num_kv_heads)
+    return max(1, min(8, tiles // 2, 296 // ctas))
+
+
 _FORCE_GENERIC_WINDOW = os.environ.get("CUINFER_B200_WINDOW_ATTENTION", "") == "generic"
 
 
 def window_attention(q: torch.Tensor, out: torch.Tensor, kv: PagedKV, ctx: StepContext, num_heads: int, num_kv_heads: int,
                      dim: int, vdim: int, scale: float, softcap: float, window: int, keep_first: int) -> None:
     """Attention over cached [key | value] rows with a capped score and a window that keeps the first tokens: bfloat16
-    steps whose sizes the tensor-core kernel takes run there, decode steps too (a CTA per request and key/value head
-    walks the window in 64-key tiles; the all-sizes kernel, a warp per token and head with one key per lane, measured 20
-    times slower at a window of 1 024 keys of 128 values); float32 and every other size run the all-sizes kernel.  ``CUINFER_B200_WINDOW_ATTENTION=generic``
+    steps whose sizes the tensor-core kernel takes run there, decode steps too (the window's 64-key tiles shared out to
+    several CTAs, see ``window_decode_splits``; the all-sizes kernel, a warp per token and head with one key per lane,
+    measured 16 times slower at a window of 1 024 keys of 128 values); float32 and every other size run the all-sizes kernel.  ``CUINFER_B200_WINDOW_ATTENTION=generic``
     keeps everything on the all-sizes kernel (for comparisons)."""
     if (q.dtype == torch.bfloat16 and not _FORCE_GENERIC_WINDOW and q.stride(0) % 8 == 0
             and kernels.window_attention_mma_supports(dim, vdim, num_heads, num_kv_heads)):
         kernels.window_attention_mma(q, out, kv.cache, kv.group.block_table, ctx.query_start_loc, ctx.seq_lens,
-                                     ctx.query_lens_for_launch(), num_heads, num_kv_heads, dim, vdim, scale, softcap, window, keep_first)
+                                     ctx.query_lens_for_launch(), num_heads, num_kv_heads, dim, vdim, scale, softcap, window, keep_first,
+                                     splits=window_decode_splits(ctx, num_kv_heads, window, keep_first))
         return
     kernels.window_attention_generic(q, out, kv.cache, kv.group.block_table, ctx.positions, ctx.token_request, num_heads,
                                      num_kv_heads, dim, vdim, scale, softcap, window, keep_first)

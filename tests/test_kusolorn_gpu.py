@@ -335,7 +335,7 @@ def test_routed_experts_with_the_clamped_gate(dtype, rows, width, ff, experts, t
     _close(out, want, dtype, "weighted sum of the chosen experts", tol=None if dtype == torch.float32 else 3e-2)
 
 
-def _attention_case(dtype, H, G, d, dv, lengths, new, page, seed, window, keep, cap, sharpen=None, tensor_cores=False):
+def _attention_case(dtype, H, G, d, dv, lengths, new, page, seed, window, keep, cap, sharpen=None, tensor_cores=False, splits=1):
     """Requests of ``lengths`` tokens whose last ``new`` are this step's queries, over a cache of random keys and values
     on shuffled pages; kernel output and the plain result from the same cached rows.  ``sharpen[t] = j`` makes query t's
     score with key j of its request stand out."""
@@ -385,7 +385,7 @@ def _attention_case(dtype, H, G, d, dv, lengths, new, page, seed, window, keep, 
         for k in new:
             qsl.append(qsl[-1] + k)
         kernels.window_attention_mma(_dev(q.reshape(T, H * d), dtype), out, cache.cuda(), table.cuda(), _ints(qsl), _ints(lengths),
-                                     [T + 64] + [1] * (len(new) - 1), H, G, d, dv, scale, cap or 0.0, window, keep)
+                                     [T + 64] + [1] * (len(new) - 1), H, G, d, dv, scale, cap or 0.0, window, keep, splits=splits)
     else:
         kernels.window_attention_generic(_dev(q.reshape(T, H * d), dtype), out, cache.cuda(), table.cuda(), _ints(pos), _ints(treq),
                                          H, G, d, dv, scale, cap or 0.0, window, keep)
@@ -432,6 +432,22 @@ def test_attention_on_the_tensor_cores(d, dv, H, G):
     for j in (n - 1 - window + 1, n - 1 - window, keep - 1, keep, 0, 63, 64, n - 1):
         got, want = _attention_case(dtype, H, G, d, dv, [n, 50], [100, 2], 16, j, window, keep, 25.0, sharpen={99: j}, tensor_cores=True)
         _close(got, want, dtype, f"query {n - 1} with key {j} standing out")
+
+
+@pytest.mark.parametrize("splits", [2, 3, 8])
+def test_decode_steps_share_a_window_over_several_ctas(splits):
+    """Single decoded tokens whose key tiles are split over CTAs and merged: windows longer and shorter than the context,
+    more splits than a request has tiles (CTAs without a tile), a key made to stand out in the first, a middle and the
+    last split and among the kept tokens."""
+    dtype = torch.bfloat16
+    for window, keep, cap in ((0, 0, 0.0), (300, 6, 30.0), (40, 100, 0.0)):
+        got, want = _attention_case(dtype, 8, 2, 64, 64, [700, 1, 97, 333], [1, 1, 1, 1], 16, 5 + window, window, keep, cap,
+                                    tensor_cores=True, splits=splits)
+        _close(got, want, dtype, f"decode with window {window} keeping {keep} over {splits} splits")
+    n, window, keep = 640, 300, 6
+    for j in (n - window, n - window - 1, keep - 1, keep, 400, n - 65, n - 1):
+        got, want = _attention_case(dtype, 4, 2, 128, 64, [n, 20], [1, 1], 16, j, window, keep, 25.0, sharpen={0: j}, tensor_cores=True, splits=splits)
+        _close(got, want, dtype, f"query {n - 1} with key {j} standing out over {splits} splits")
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
