@@ -22,7 +22,7 @@ def attention(heads=4, kv_heads=2, dim=16, vdim=8, window=12, keep=3, v_mix=True
     if rot:
         m["rot"] = {"base": 1000.0, "dims": rot}
         if scaling:
-            m["rot"]["scaling"] = {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 64}
+            m["rot"]["scaling"] = {"factor": 6.0, "low": 1.0, "high": 3.0, "original": 64}
     return {"type": "attention", "mixer": m, "mlp": {"kind": "dense", "ff": 40}}
 
 
@@ -90,14 +90,14 @@ def test_scaled_frequencies_follow_the_plain_rule():
     from cuinfer_b200.parts.position import RotaryInterleaved
     from cuinfer_b200.parts.spec import PartSpec
 
-    for dims, base, scaling in ((8, 1000.0, (4.0, 1.0, 4.0, 64)), (32, 1e6, (8.0, 2.0, 6.0, 512)), (6, 50.0, None)):
+    for dims, base, scaling in ((8, 1000.0, (6.0, 1.0, 3.0, 64)), (32, 2e5, (8.0, 2.0, 6.0, 512)), (6, 50.0, None)):
         part = RotaryInterleaved(PartSpec("rope_interleaved", theta=base, rotary_dim=dims, scaling=scaling), hidden_size=8,
                                  prefix="x", dtype=torch.float32)
         raw = dict(zip(("factor", "low", "high", "original"), scaling)) if scaling else None
         want = torch.tensor(plain.rotary_frequencies(base, dims, raw), dtype=torch.float64)
         assert torch.allclose(part.host_frequencies().double(), want, rtol=1e-6, atol=0)
-    kinds = {round(f / (1000.0 ** (-2.0 * i / 8)), 6) for i, f in enumerate(plain.rotary_frequencies(1000.0, 8, {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 64}))}
-    assert 1.0 in kinds and 0.25 in kinds and len(kinds) >= 3, "the test's constants must reach all three branches"
+    kinds = {round(f / (1000.0 ** (-2.0 * i / 8)), 6) for i, f in enumerate(plain.rotary_frequencies(1000.0, 8, {"factor": 6.0, "low": 1.0, "high": 3.0, "original": 64}))}
+    assert 1.0 in kinds and round(1 / 6, 6) in kinds and len(kinds) >= 3, "the test's constants must reach all three branches"
 
 
 def test_pages_behind_a_window_are_given_back_except_those_of_the_kept_tokens():

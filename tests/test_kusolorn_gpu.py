@@ -58,12 +58,12 @@ LATE = _config(300, 128, [
     _attention(4, 2, 32, 48, 0.3, window=33, keep=40, rot={"base": 10000.0, "dims": 32}, softcap=8.0, v_mix=True, mlp=None),
 ])
 # sizes in multiples of 64, for the tensor-core paths in bfloat16 (grouped experts, tcgen05 projections)
-WIDE = _config(512, 256, [
-    _attention(8, 2, 64, 64, 0.2, window=48, keep=5, rot={"base": 1e6, "dims": 32, "scaling": {"factor": 4.0, "low": 1.0, "high": 8.0, "original": 256}},
+WIDE = _config(768, 384, [
+    _attention(12, 4, 64, 64, 0.2, window=48, keep=5, rot={"base": 5e5, "dims": 16, "scaling": {"factor": 4.0, "low": 1.0, "high": 8.0, "original": 256}},
                softcap=40.0, v_mix=True, mlp=_moe(6, 2, 128, 1.0)),
-    {"type": "delta", "mixer": {"heads": 4, "kv_heads": 2, "dim": 64, "vdim": 64, "conv": 3}, "mlp": {"kind": "dense", "ff": 512}},
-    _attention(4, 2, 128, 64, 0.12, window=64, keep=16, rot={"base": 1e4, "dims": 64}, v_mix=True, mlp=_moe(8, 3, 64, 3.0)),
-    {"type": "mlstm", "mixer": {"heads": 2, "dim": 64, "vdim": 128, "gate_cap": 12.0}, "mlp": {"kind": "dense", "ff": 256}},
+    {"type": "delta", "mixer": {"heads": 4, "kv_heads": 2, "dim": 64, "vdim": 64, "conv": 4}, "mlp": {"kind": "dense", "ff": 768}},
+    _attention(4, 4, 128, 64, 0.12, window=64, keep=16, rot={"base": 1e4, "dims": 64}, v_mix=True, mlp=_moe(8, 3, 64, 3.0)),
+    {"type": "mlstm", "mixer": {"heads": 3, "dim": 64, "vdim": 128, "gate_cap": 9.0}, "mlp": {"kind": "dense", "ff": 384}},
 ], side=16)
 MODELS = {"odd": (ODD, 16, 21), "late": (LATE, 32, 22), "wide": (WIDE, 16, 23)}
 
