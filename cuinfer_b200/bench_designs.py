@@ -58,7 +58,7 @@ def kusolorn_config(s: dict) -> dict:
     attention with the Qwen3 arm's head counts and head size, the gated delta rule, the matrix memory; a dense
     feed-forward first and routed experts after it; the per-layer token input."""
     attention = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["head_dim"], "vdim": s["head_dim"], "scale": s["head_dim"] ** -0.5,
-                 "softcap": 50.0, "v_mix": True, "mask": {"size": s["window"], "keep_first": s["keep_first"]},
+                 "softcap": 30.0, "v_mix": True, "mask": {"size": s["window"], "keep_first": s["keep_first"]},
                  "rot": {"base": 1000000.0, "dims": s["head_dim"] // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
     delta = {"heads": s["delta_heads"], "kv_heads": s["delta_kv_heads"], "dim": s["delta_dim"], "vdim": s["delta_vdim"], "conv": 4}
     memory = {"heads": s["memory_heads"], "dim": s["memory_dim"], "vdim": s["memory_vdim"], "gate_cap": 15.0}
